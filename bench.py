@@ -1,0 +1,363 @@
+"""Benchmark of the operator hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Headline workload: large-batch paged decode attention at Qwen3-8B head shapes -- 256 sequences,
+context lengths uniform in [512, 8192], 32 query / 8 KV heads, head_dim 128, page 256, bf16,
+seeded random block tables over a pool sized to fit (about 4.5 GB of live K/V).  With N > 1
+(launched by torch.distributed.run, one rank per GPU) the KV heads are split over the ranks as
+nano-vLLM's tensor parallelism splits them; no rank talks to another inside the op.
+
+One step = one pass of the op over the whole batch.  The timed region is K back-to-back steps
+between CUDA events on the launching stream, bracketed by a barrier and a device synchronise;
+the reported time is the maximum over ranks.  The K/V pool is far larger than L2, so no flush
+is needed between steps.  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the CPU restatement of the reference operator (the checker under
+oracle/) on the host cores for the same metric, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from nano_vllm_ninetoothed_b200 import workloads as W  # noqa: E402
+
+METRIC = "paged_decode_attn_hbm_gbs"
+UNIT = "GB/s"
+HQ, HKV, HEAD_DIM, PAGE = 32, 8, 128, 256
+WORKLOAD = ("paged decode attention, Qwen3-8B heads (32q/8kv, d128), 256 seqs, ctx U[512,8192], "
+            "page 256, bf16")
+
+# DRAM bytes of one full-size launch of the decode kernel on one GPU, from the ncu capture
+# summarised under profiles/ (None until a capture exists for the current kernel).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def peaks() -> dict:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        p = json.loads(f.read_text())
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples taken while the timed region runs (read-only)."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu_index), "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.lines = []
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+                out, _ = self.proc.communicate()
+            self.lines = [l for l in out.splitlines() if l.strip()]
+
+    def summary(self) -> dict:
+        sm, smax, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax = max(smax, float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def timed_steps(fn, steps: int, warmup: int, world: int, sampler: ClockSampler | None):
+    """W untimed calls, then K calls between two events; returns max-over-ranks milliseconds."""
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx = sampler if sampler is not None else _Null()
+    with ctx:
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def cpu_baseline_decode(lens: list[int], budget_s: float = 12.0) -> dict:
+    """The oracle's paged decode on the host cores over the first sequences of the workload."""
+    from oracle import mops_oracle as O
+    n_seq = 24
+    sample = lens[:n_seq]
+    case = W.make_decode_case(seed=0, lens=sample, hq=HQ, hkv=HKV, page=PAGE)
+    nbytes = case.algorithmic_bytes()
+    call = lambda: O.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                             cache_seqlens=case.cache_seqlens,
+                                             block_table=case.block_table,
+                                             softmax_scale=case.softmax_scale)
+    call()
+    times, t_all = [], time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - t_all < budget_s and len(times) < 20):
+        t0 = time.perf_counter()
+        call()
+        times.append(time.perf_counter() - t0)
+    best = statistics.median(times)
+    return {"value": nbytes / best / 1e9, "unit": UNIT, "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"first {n_seq} of the 256 sequences ({nbytes / 1e6:.0f} MB of K/V), "
+                      f"median of {len(times)} runs, host has {os.cpu_count()} cpus",
+            "seconds_per_pass": best}
+
+
+def run_reference(args) -> None:
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    lens = W.config_lens("decode_8b")
+    steps = max(1, args.steps)
+    base = cpu_baseline_decode(lens, budget_s=min(60.0, 2.0 * steps))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": base["seconds_per_pass"] * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": base["sample"]},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def bench_side_ops(mops, dev, rank: int, world: int, steps: int, warmup: int, pk: dict) -> dict:
+    """The other operators of the path at their benchmark shapes (device-resident inputs,
+    rotating over copies that together exceed L2 where one copy would fit in it)."""
+    out = {}
+
+    def rotate(make, n_copies):
+        sets = [make(i) for i in range(n_copies)]
+        state = {"i": 0}
+
+        def step(fn):
+            def run():
+                fn(*sets[state["i"] % n_copies])
+                state["i"] += 1
+            return run
+        return step
+
+    # varlen causal prefill, Qwen3-8B heads, 16 sequences in [256, 4096], KV-head sharded
+    lens = W.config_lens("prefill_8b")
+    full = W.make_prefill_case(seed=0, lens=lens, hq=HQ, hkv=HKV, device=dev)
+    p = W.shard_prefill_case(full, rank, world) if world > 1 else full
+    del full
+    fn = lambda: mops.flash_attn_varlen_func(p.q, p.k, p.v, max_seqlen_q=p.max_seqlen,
+                                             cu_seqlens_q=p.cu_seqlens, max_seqlen_k=p.max_seqlen,
+                                             cu_seqlens_k=p.cu_seqlens,
+                                             softmax_scale=p.softmax_scale, causal=True)
+    ms = timed_steps(fn, steps, warmup, world, None) / steps
+    flops = W.prefill_flops(lens, HQ, HEAD_DIM)
+    tf = flops / (ms * 1e-3) / 1e12
+    out["varlen_prefill"] = {"workload": "Qwen3-8B heads, 16 seqs U[256,4096], causal, bf16",
+                             "tflops": tf, "ms": ms, "frac_of_bf16_peak": tf / world / pk["bf16_tflops"],
+                             "sharded_by_kv_head": world > 1}
+    del p
+    if world > 1:
+        return out
+    # prefill-side bandwidth ops at Qwen3-0.6B shapes (T ~ 8.1k tokens); six input sets rotate
+    t = sum(W.config_lens("prefill_small"))
+    step = rotate(lambda i: W.make_store_case(seed=i, n_tokens=t, hkv=8, num_blocks=128, device=dev), 6)
+    ms = timed_steps(step(lambda k, v, kc, vc, s: mops.store_kvcache(k, v, kc, vc, s)), steps * 6,
+                     warmup, 1, None) / (steps * 6)
+    gbs = W.store_bytes(t, 8, 128) / (ms * 1e-3) / 1e9
+    out["store_kvcache"] = {"tokens": t, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
+    step = rotate(lambda i: W.make_rms_case(seed=i, rows=t, hidden=1024, device=dev), 6)
+    ms = timed_steps(step(lambda x, r, w: mops.add_rms_forward(x, r, w, 1e-6)), steps * 6,
+                     warmup, 1, None) / (steps * 6)
+    gbs = W.add_rms_bytes(t, 1024) / (ms * 1e-3) / 1e9
+    out["add_rms_forward"] = {"rows": t, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
+    ids0, table = W.make_embedding_case(seed=0, n_ids=t, device=dev)
+    g = torch.Generator().manual_seed(3)
+    id_sets = [torch.randint(0, 151936, (t,), generator=g).to(dev) for _ in range(6)]
+    state = {"i": 0}
+
+    def emb():
+        mops.embedding(id_sets[state["i"] % 6], table)
+        state["i"] += 1
+    ms = timed_steps(emb, steps * 6, warmup, 1, None) / (steps * 6)
+    gbs = W.embedding_bytes(t, 1024) / (ms * 1e-3) / 1e9
+    out["embedding"] = {"ids": t, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
+    return out
+
+
+def run_ours(args) -> None:
+    import torch.distributed as dist
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; this backend has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.gpus != world:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    from nano_vllm_ninetoothed_b200 import _cabi, mops
+    if _cabi.lib.b200mops_device_supported(local) != 0:
+        raise SystemExit("libb200mops.so contains sm_100a code only; this device is not a B200")
+    pk = peaks()
+
+    lens = W.config_lens("decode_8b")
+    lo, hi = W.kv_head_range(HKV, rank, world)
+    hkv_r, hq_r = hi - lo, (hi - lo) * (HQ // HKV)
+    case = W.make_decode_case(seed=rank, lens=lens, hq=hq_r, hkv=hkv_r, page=PAGE, device=dev,
+                              cache_on_device=True)
+    bytes_rank = case.algorithmic_bytes()
+    bytes_total = W.decode_bytes(torch.tensor(lens), HQ, HKV, HEAD_DIM, PAGE)
+
+    def step():
+        return mops.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                            cache_seqlens=case.cache_seqlens,
+                                            block_table=case.block_table,
+                                            softmax_scale=case.softmax_scale, causal=True)
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    total_ms = timed_steps(step, args.steps, args.warmup, world, sampler)
+    ms_step = total_ms / args.steps
+    value = bytes_total / (ms_step * 1e-3) / 1e9
+    clocks = sampler.summary() if sampler is not None else {}
+
+    # end to end through the public op with host buffers: every step copies q, the lengths and
+    # the block table from pinned host memory and reads the output back.  The K/V pool is the
+    # engine's device-resident state (allocated once by the model runner), not a step input.
+    q_h = case.q.cpu().pin_memory()
+    lens_h = case.cache_seqlens.cpu().pin_memory()
+    tbl_h = case.block_table.cpu().pin_memory()
+    o_h = torch.empty_like(q_h).pin_memory()
+
+    def e2e_step():
+        q_d = q_h.to(dev, non_blocking=True)
+        l_d = lens_h.to(dev, non_blocking=True)
+        t_d = tbl_h.to(dev, non_blocking=True)
+        o = mops.flash_attn_with_kvcache(q_d, case.k_cache, case.v_cache, cache_seqlens=l_d,
+                                         block_table=t_d, softmax_scale=case.softmax_scale,
+                                         causal=True)
+        o_h.copy_(o, non_blocking=True)
+
+    e2e_ms = timed_steps(e2e_step, args.steps, args.warmup, world, None) / args.steps
+    h2d = q_h.numel() * 2 + lens_h.numel() * 4 + tbl_h.numel() * 4
+    d2h = o_h.numel() * 2
+    e2e_value = bytes_total / (e2e_ms * 1e-3) / 1e9
+
+    status = mops.device_status()
+    side = bench_side_ops(mops, dev, rank, world, max(3, min(args.steps, 10)), 3, pk)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    achieved = bytes_rank / (ms_step * 1e-3) / 1e9      # per-GPU kernel bandwidth
+    chunk = _cabi.lib.b200mops_paged_decode_auto_chunk(256, hkv_r, PAGE, case.block_table.shape[1])
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sharding": f"kv heads split over {world} rank(s)",
+                   "kv_bytes_total": bytes_total, "chunk_tokens": chunk,
+                   "l2": "inputs larger than L2 (>=570 MB of K/V per GPU per step), no flush"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": UNIT,
+                     "frac": achieved / pk["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "peak_source": pk["source"],
+                     "note": "duration = one step (decode kernel + split combine kernel)"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+        "device_status": status,
+        "ops": side,
+    }
+    if world == 1:
+        line["cpu_baseline"] = {k: v for k, v in cpu_baseline_decode(lens).items()
+                                if k != "seconds_per_pass"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

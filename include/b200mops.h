@@ -1,0 +1,244 @@
+/*
+ * b200mops.h -- C ABI of the B200 (sm_100a) operator backend for the `mops`
+ * library that nano-vLLM's layers call.
+ *
+ * Every entry point takes plain device pointers, element counts, element
+ * strides and a CUDA stream (passed as void* so that this header needs no CUDA
+ * include).  Nothing here allocates, synchronises or creates streams: outputs
+ * and split-K scratch are owned by the caller, every launch goes to the given
+ * stream, and each function returns a b200mops_status (0 = success) before or
+ * right after its launch.  Argument errors are reported before anything is
+ * launched.  Strides are in ELEMENTS of the tensor's dtype unless stated.
+ *
+ * The citation on each function names the reference operator it stands in for
+ * (paths are relative to the reference project's root).
+ */
+#ifndef B200MOPS_H
+#define B200MOPS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOPS_ABI_VERSION 1
+
+typedef enum b200mops_status {
+    B200MOPS_OK = 0,
+    B200MOPS_ERR_NULL_POINTER = 1,   /* a required pointer is NULL */
+    B200MOPS_ERR_DTYPE = 2,          /* dtype code not supported by this op */
+    B200MOPS_ERR_SHAPE = 3,          /* negative / inconsistent sizes */
+    B200MOPS_ERR_STRIDE = 4,         /* stride contract violated */
+    B200MOPS_ERR_ALIGNMENT = 5,      /* pointer or stride not 16-byte aligned where required */
+    B200MOPS_ERR_HEAD_DIM = 6,       /* head_dim not supported by the attention kernels */
+    B200MOPS_ERR_PAGE_SIZE = 7,      /* KV page size not a multiple of the token tile */
+    B200MOPS_ERR_GQA = 8,            /* q heads not a multiple of kv heads, or group too large */
+    B200MOPS_ERR_WORKSPACE = 9,      /* scratch buffer missing or too small */
+    B200MOPS_ERR_TENSOR_MAP = 10,    /* TMA descriptor could not be encoded */
+    B200MOPS_ERR_LAUNCH = 11,        /* the CUDA launch itself failed */
+    B200MOPS_ERR_DEVICE = 12,        /* current device is not compute capability 10.x */
+    B200MOPS_ERR_UNSUPPORTED = 13,   /* valid request that this build does not implement */
+    B200MOPS_ERR_TOO_LARGE = 14      /* size exceeds a fixed capacity of the entry point */
+} b200mops_status;
+
+typedef enum b200mops_dtype {
+    B200MOPS_BF16 = 0,
+    B200MOPS_F16 = 1,
+    B200MOPS_F32 = 2
+} b200mops_dtype;
+
+/* Bits that kernels OR into the optional device-side `status_word` (an int32
+ * in global memory that the caller zeroes and may read back later).  Kernels
+ * never trap: they skip the offending access and record why. */
+#define B200MOPS_DEV_BAD_SLOT      0x1  /* slot_mapping entry outside [-1, num_slots) */
+#define B200MOPS_DEV_BAD_TOKEN_ID  0x2  /* embedding id outside [0, vocab) */
+#define B200MOPS_DEV_BAD_PAGE      0x4  /* block_table entry outside [0, num_blocks) */
+#define B200MOPS_DEV_WAIT_TIMEOUT  0x8  /* a bounded mbarrier wait gave up */
+
+/* Human-readable text for a b200mops_status. Never NULL. */
+const char* b200mops_strerror(int status);
+
+/* Returns B200MOPS_ABI_VERSION of the loaded library. */
+int b200mops_abi_version(void);
+
+/* B200MOPS_OK when `device` (a CUDA ordinal) is compute capability 10.x,
+ * B200MOPS_ERR_DEVICE otherwise. The library contains sm_100a code only. */
+int b200mops_device_supported(int device);
+
+/* ------------------------------------------------------------------------
+ * store_kvcache: scatter this step's K and V rows into the paged caches.
+ *   for i < n_tokens: s = slot_mapping[i]; if s == -1 skip;
+ *     k_cache[s*cache_slot_stride : +row_elems] = key[i*key_stride0 : +row_elems]
+ *     (same for value / v_cache)
+ * Stands in for mops.store_kvcache: mops/triton/attention.py:7-38 (kernel and
+ * its stride asserts), forwarded by mops/torch/ops.py:62-65, called from
+ * nanovllm/layers/attention.py:28-29.  Slots outside [-1, num_slots) are
+ * skipped and flagged in status_word (the reference would write out of bounds).
+ * ---------------------------------------------------------------------- */
+int b200mops_store_kvcache(const void* key, const void* value,
+                           int64_t key_stride0, int64_t value_stride0,
+                           void* k_cache, void* v_cache, int64_t cache_slot_stride,
+                           const int32_t* slot_mapping, int64_t n_tokens,
+                           int64_t row_elems, int64_t num_slots,
+                           int dtype, int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------
+ * embedding: out[i, :] = weight[ids[i], :]   (bit-exact row gather).
+ * Stands in for mops.embedding: mops/torch/ops.py:57-59, called from
+ * nanovllm/layers/embed_head.py:37-45 with int64 ids.  ids outside
+ * [0, vocab) produce a zero row and set B200MOPS_DEV_BAD_TOKEN_ID.
+ * `out` is contiguous [n_ids, hidden].
+ * ---------------------------------------------------------------------- */
+int b200mops_embedding(const int64_t* ids, int64_t n_ids,
+                       const void* weight, int64_t vocab, int64_t hidden,
+                       int64_t weight_stride0, void* out,
+                       int dtype, int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------
+ * rms_forward: y = cast(cast(x * rsqrt(mean(x^2) + eps)) * w) over the last
+ * dim, arithmetic in fp32, both casts to the tensor dtype.
+ * Rows are addressed as x[i0*x_stride0 + i1*x_stride1 + 0..n) for
+ * i0 < rows0, i1 < rows1, which covers the strided [T, H, 128] q/k-norm views
+ * of the fused qkv activation (nanovllm/models/qwen3.py:76-77) and plain
+ * [T, n] inputs (rows1 = 1).  `out` is contiguous [rows0*rows1, n].
+ * Stands in for mops.rms_forward: mops/torch/ops.py:9-16, called from
+ * nanovllm/layers/layernorm.py:17-21.
+ * ---------------------------------------------------------------------- */
+int b200mops_rmsnorm(const void* x, int64_t rows0, int64_t rows1,
+                     int64_t x_stride0, int64_t x_stride1,
+                     const void* weight, float eps, void* out, int64_t n,
+                     int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * add_rms_forward: s = f32(x) + f32(residual); residual_out = cast(s);
+ *   out = cast(cast(s * rsqrt(mean(s^2) + eps)) * w), the variance taken from
+ *   the unrounded fp32 sum.
+ * Stands in for mops.add_rms_forward: mops/torch/ops.py:18-30, called from
+ * nanovllm/layers/layernorm.py:24-29.  `out` and `residual_out` are
+ * contiguous [rows, n] and may alias x / residual respectively.
+ * ---------------------------------------------------------------------- */
+int b200mops_add_rmsnorm(const void* x, const void* residual, int64_t rows, int64_t n,
+                         int64_t x_stride0, int64_t residual_stride0,
+                         const void* weight, float eps,
+                         void* out, void* residual_out,
+                         int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * siluAndMul: out = cast(cast(silu(f32(x))) * y); x and y are [rows, n] views
+ * with unit inner stride (the two halves of the gate_up activation).
+ * Stands in for mops.siluAndMul: mops/torch/ops.py:32-34, called from
+ * nanovllm/layers/activation.py:14-16.
+ * ---------------------------------------------------------------------- */
+int b200mops_silu_mul(const void* x, const void* y, int64_t rows, int64_t n,
+                      int64_t x_stride0, int64_t y_stride0, void* out,
+                      int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * apply_rotary_emb (NeoX half-split): with x = [x1 | x2] along head_dim,
+ *   y1 = x1*cos - x2*sin, y2 = x2*cos + x1*sin in fp32, cast to dtype.
+ * x is [tokens, heads, head_dim] with strides (x_stride0, x_stride1, 1);
+ * cos/sin are fp32 rows of head_dim/2 values, row t at cos + t*cs_stride0;
+ * `out` is contiguous.  Stands in for mops.apply_rotary_emb:
+ * mops/torch/ops.py:45-54, called from nanovllm/layers/rotary_embedding.py:27-37.
+ * ---------------------------------------------------------------------- */
+int b200mops_rope_neox(const void* x, int64_t tokens, int64_t heads, int64_t head_dim,
+                       int64_t x_stride0, int64_t x_stride1,
+                       const float* cos, const float* sin, int64_t cs_stride0,
+                       void* out, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * sampler_forward: out[r] = argmax_j( f32(logits[r, j]) / temperatures[r] ),
+ * lowest index on ties -- what argmax(softmax(logits / T)) returns for T > 0.
+ * Stands in for mops.sampler_forward: mops/torch/ops.py:37-43, called from
+ * nanovllm/layers/sampler.py:11-12.  `workspace` holds the per-row partial
+ * maxima; size it with b200mops_sample_argmax_workspace_bytes(rows, vocab).
+ * ---------------------------------------------------------------------- */
+size_t b200mops_sample_argmax_workspace_bytes(int64_t rows, int64_t vocab);
+int b200mops_sample_argmax(const void* logits, int64_t rows, int64_t vocab, int64_t stride0,
+                           const float* temperatures, int64_t* out,
+                           void* workspace, size_t workspace_bytes,
+                           int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Paged decode attention (one query token per sequence).
+ *   out[b, h, :] = softmax(scale * q[b, h, :] . K_b[:len_b, h / G]^T) . V_b[:len_b, h / G]
+ * where token t of sequence b lives at cache[block_table[b, t / page], t % page],
+ * G = hq / hkv, len_b = cache_seqlens[b].  len_b == 0 gives a zero row.  Only
+ * the first ceil(len_b / page) table entries of a row are read.
+ * q/out: [batch, hq, head_dim], unit inner stride.  Caches:
+ * [num_blocks, page, hkv, head_dim] with the given block/token/head strides.
+ * The KV length is cut into chunks of `chunk_tokens` (0 = pick automatically);
+ * `workspace` receives the per-chunk partial results and must hold
+ * b200mops_paged_decode_workspace_bytes(...) bytes for the same arguments.
+ * Stands in for mops.flash_attn_with_kvcache: mops/torch/ops.py:74-76
+ * (semantics spelled out at :78-125), called from
+ * nanovllm/layers/attention.py:40-42 with inputs built at
+ * nanovllm/engine/model_runner.py:164-180,120-124.
+ * ---------------------------------------------------------------------- */
+typedef struct b200mops_paged_decode_args {
+    const void* q;            int64_t q_stride_b, q_stride_h;
+    void* out;                int64_t out_stride_b, out_stride_h;
+    const void* k_cache;      int64_t k_stride_block, k_stride_token, k_stride_head;
+    const void* v_cache;      int64_t v_stride_block, v_stride_token, v_stride_head;
+    const int32_t* cache_seqlens;           /* [batch] */
+    const int32_t* block_table;             /* [batch, max_blocks_per_seq] */
+    int64_t table_stride0;
+    int64_t batch, hq, hkv, head_dim;
+    int64_t page, num_blocks, max_blocks_per_seq;
+    float softmax_scale;
+    int32_t chunk_tokens;                   /* 0 = automatic */
+    void* workspace;          size_t workspace_bytes;
+    int32_t* status_word;                   /* optional */
+    int32_t dtype;
+} b200mops_paged_decode_args;
+
+size_t b200mops_paged_decode_workspace_bytes(int64_t batch, int64_t hq, int64_t hkv,
+                                             int64_t head_dim, int64_t page,
+                                             int64_t max_blocks_per_seq, int32_t chunk_tokens);
+/* The chunk length the library would use for these sizes when chunk_tokens == 0. */
+int32_t b200mops_paged_decode_auto_chunk(int64_t batch, int64_t hkv, int64_t page,
+                                         int64_t max_blocks_per_seq);
+int b200mops_paged_decode(const b200mops_paged_decode_args* args, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Variable-length causal prefill attention over packed tokens.
+ *   per sequence b, head h: softmax(scale * Q_b K_b^T + causal mask) V_b with
+ *   KV head h / G; the causal mask is aligned to the bottom-right corner
+ *   (query i of len_q sees keys j <= i + len_k - len_q), which is the plain
+ *   lower triangle when cu_seqlens_q == cu_seqlens_k.
+ * q/out: [total_q, hq, head_dim]; k, v: [total_k, hkv, head_dim] with the
+ * given token/head strides and unit inner stride (v is a strided slice of the
+ * qkv activation: nanovllm/models/qwen3.py:75-78).  When block_table != NULL,
+ * k and v are the paged caches [num_blocks, page, hkv, head_dim] instead
+ * (prefix-cache prefill) and k/v_stride_block apply.
+ * Stands in for mops.flash_attn_varlen_func: mops/torch/ops.py:70-72, called
+ * from nanovllm/layers/attention.py:31-37 with inputs built at
+ * nanovllm/engine/model_runner.py:126-162.
+ * ---------------------------------------------------------------------- */
+typedef struct b200mops_varlen_prefill_args {
+    const void* q;            int64_t q_stride_t, q_stride_h;
+    const void* k;            int64_t k_stride_t, k_stride_h, k_stride_block;
+    const void* v;            int64_t v_stride_t, v_stride_h, v_stride_block;
+    void* out;                int64_t out_stride_t, out_stride_h;
+    const int32_t* cu_seqlens_q;            /* [batch + 1] */
+    const int32_t* cu_seqlens_k;            /* [batch + 1] */
+    const int32_t* block_table;             /* NULL, or [batch, max_blocks_per_seq] */
+    int64_t table_stride0;
+    int64_t batch, total_q, total_k;
+    int64_t max_seqlen_q, max_seqlen_k;
+    int64_t hq, hkv, head_dim;
+    int64_t page, num_blocks, max_blocks_per_seq;   /* paged K/V only */
+    float softmax_scale;
+    int32_t causal;
+    int32_t* status_word;                   /* optional */
+    int32_t dtype;
+} b200mops_varlen_prefill_args;
+
+int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOPS_H */

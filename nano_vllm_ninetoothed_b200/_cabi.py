@@ -1,0 +1,126 @@
+"""ctypes binding of `lib/libb200mops.so` (the C ABI declared in `include/b200mops.h`).
+
+There is no fallback: if the shared library is missing or fails to load, importing this
+module raises, and so does every op of the package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libb200mops.so"
+
+BF16, F16, F32 = 0, 1, 2
+
+DEV_BAD_SLOT, DEV_BAD_TOKEN_ID, DEV_BAD_PAGE, DEV_WAIT_TIMEOUT = 0x1, 0x2, 0x4, 0x8
+
+# Every symbol the header declares; tests check that the library exports all of them.
+EXPORTED_SYMBOLS = (
+    "b200mops_strerror",
+    "b200mops_abi_version",
+    "b200mops_device_supported",
+    "b200mops_store_kvcache",
+    "b200mops_embedding",
+    "b200mops_rmsnorm",
+    "b200mops_add_rmsnorm",
+    "b200mops_silu_mul",
+    "b200mops_rope_neox",
+    "b200mops_sample_argmax_workspace_bytes",
+    "b200mops_sample_argmax",
+    "b200mops_paged_decode_workspace_bytes",
+    "b200mops_paged_decode_auto_chunk",
+    "b200mops_paged_decode",
+    "b200mops_varlen_prefill",
+)
+
+_i64, _i32, _f32, _vp, _sz = C.c_int64, C.c_int32, C.c_float, C.c_void_p, C.c_size_t
+
+
+class PagedDecodeArgs(C.Structure):
+    """Mirror of `b200mops_paged_decode_args`."""
+    _fields_ = [
+        ("q", _vp), ("q_stride_b", _i64), ("q_stride_h", _i64),
+        ("out", _vp), ("out_stride_b", _i64), ("out_stride_h", _i64),
+        ("k_cache", _vp), ("k_stride_block", _i64), ("k_stride_token", _i64), ("k_stride_head", _i64),
+        ("v_cache", _vp), ("v_stride_block", _i64), ("v_stride_token", _i64), ("v_stride_head", _i64),
+        ("cache_seqlens", _vp), ("block_table", _vp), ("table_stride0", _i64),
+        ("batch", _i64), ("hq", _i64), ("hkv", _i64), ("head_dim", _i64),
+        ("page", _i64), ("num_blocks", _i64), ("max_blocks_per_seq", _i64),
+        ("softmax_scale", _f32), ("chunk_tokens", _i32),
+        ("workspace", _vp), ("workspace_bytes", _sz),
+        ("status_word", _vp), ("dtype", _i32),
+    ]
+
+
+class VarlenPrefillArgs(C.Structure):
+    """Mirror of `b200mops_varlen_prefill_args`."""
+    _fields_ = [
+        ("q", _vp), ("q_stride_t", _i64), ("q_stride_h", _i64),
+        ("k", _vp), ("k_stride_t", _i64), ("k_stride_h", _i64), ("k_stride_block", _i64),
+        ("v", _vp), ("v_stride_t", _i64), ("v_stride_h", _i64), ("v_stride_block", _i64),
+        ("out", _vp), ("out_stride_t", _i64), ("out_stride_h", _i64),
+        ("cu_seqlens_q", _vp), ("cu_seqlens_k", _vp), ("block_table", _vp), ("table_stride0", _i64),
+        ("batch", _i64), ("total_q", _i64), ("total_k", _i64),
+        ("max_seqlen_q", _i64), ("max_seqlen_k", _i64),
+        ("hq", _i64), ("hkv", _i64), ("head_dim", _i64),
+        ("page", _i64), ("num_blocks", _i64), ("max_blocks_per_seq", _i64),
+        ("softmax_scale", _f32), ("causal", _i32),
+        ("status_word", _vp), ("dtype", _i32),
+    ]
+
+
+_SIGNATURES = {
+    "b200mops_strerror": (C.c_char_p, [C.c_int]),
+    "b200mops_abi_version": (C.c_int, []),
+    "b200mops_device_supported": (C.c_int, [C.c_int]),
+    "b200mops_store_kvcache": (C.c_int, [_vp, _vp, _i64, _i64, _vp, _vp, _i64, _vp, _i64, _i64, _i64,
+                                         C.c_int, _vp, _vp]),
+    "b200mops_embedding": (C.c_int, [_vp, _i64, _vp, _i64, _i64, _i64, _vp, C.c_int, _vp, _vp]),
+    "b200mops_rmsnorm": (C.c_int, [_vp, _i64, _i64, _i64, _i64, _vp, _f32, _vp, _i64, C.c_int, _vp]),
+    "b200mops_add_rmsnorm": (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _f32, _vp, _vp,
+                                       C.c_int, _vp]),
+    "b200mops_silu_mul": (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, C.c_int, _vp]),
+    "b200mops_rope_neox": (C.c_int, [_vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp,
+                                     C.c_int, _vp]),
+    "b200mops_sample_argmax_workspace_bytes": (_sz, [_i64, _i64]),
+    "b200mops_sample_argmax": (C.c_int, [_vp, _i64, _i64, _i64, _vp, _vp, _vp, _sz, C.c_int, _vp]),
+    "b200mops_paged_decode_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64, _i64, _i32]),
+    "b200mops_paged_decode_auto_chunk": (_i32, [_i64, _i64, _i64, _i64]),
+    "b200mops_paged_decode": (C.c_int, [C.POINTER(PagedDecodeArgs), _vp]),
+    "b200mops_varlen_prefill": (C.c_int, [C.POINTER(VarlenPrefillArgs), _vp]),
+}
+
+
+class B200MopsError(RuntimeError):
+    """A C-ABI call returned a non-zero b200mops_status."""
+
+    def __init__(self, fn: str, status: int, text: str):
+        super().__init__(f"{fn} failed: status {status} ({text})")
+        self.status = status
+
+
+def _load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m nano_vllm_ninetoothed_b200.build` "
+            "(this backend has no fallback path)")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    if lib.b200mops_abi_version() != 1:
+        raise ImportError("libb200mops.so ABI version does not match this package")
+    return lib
+
+
+lib = _load()
+
+
+def strerror(status: int) -> str:
+    return lib.b200mops_strerror(status).decode()
+
+
+def check(fn: str, status: int) -> None:
+    if status != 0:
+        raise B200MopsError(fn, status, strerror(status))

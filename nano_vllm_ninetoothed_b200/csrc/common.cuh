@@ -1,0 +1,88 @@
+// Shared helpers for the sm_100a kernels: dtype traits, 128-bit access,
+// launch-error mapping.  Everything in csrc/ is compiled for sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200mops.h"
+
+namespace b200mops {
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this.
+
+template <typename T> struct DType;
+template <> struct DType<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct DType<__half> {
+    static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <> struct DType<float> {
+    static __device__ __forceinline__ float to_f32(float v) { return v; }
+    static __device__ __forceinline__ float from_f32(float v) { return v; }
+};
+
+// A 16-byte packet of T (8 x 16-bit or 4 x 32-bit elements).
+template <typename T> struct alignas(16) Vec16 {
+    static constexpr int kElems = 16 / sizeof(T);
+    T v[kElems];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> load16(const T* p) {
+    Vec16<T> r;
+    *reinterpret_cast<uint4*>(&r) = *reinterpret_cast<const uint4*>(p);
+    return r;
+}
+// Read-only, no L1 allocation: streamed inputs are touched once.
+template <typename T>
+__device__ __forceinline__ Vec16<T> load16_stream(const T* p) {
+    Vec16<T> r;
+    uint4 u;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "l"(p));
+    *reinterpret_cast<uint4*>(&r) = u;
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ void store16(T* p, const Vec16<T>& r) {
+    *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(&r);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int launch_status() {
+    return cudaGetLastError() == cudaSuccess ? B200MOPS_OK : B200MOPS_ERR_LAUNCH;
+}
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline int dtype_size(int dtype) {
+    switch (dtype) {
+        case B200MOPS_BF16: case B200MOPS_F16: return 2;
+        case B200MOPS_F32: return 4;
+        default: return 0;
+    }
+}
+
+}  // namespace b200mops
+
+// Dispatch a statement over the three storage dtypes; `T` names the element type.
+#define B200MOPS_DISPATCH_DTYPE(dtype, ...)                                   \
+    switch (dtype) {                                                          \
+        case B200MOPS_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }  \
+        case B200MOPS_F16:  { using T = __half; __VA_ARGS__; break; }         \
+        case B200MOPS_F32:  { using T = float; __VA_ARGS__; break; }          \
+        default: return B200MOPS_ERR_DTYPE;                                   \
+    }

@@ -1,0 +1,251 @@
+// siluAndMul, NeoX rotary embedding and greedy sampling (argmax of logits / T).
+// All three stream their operands once with 128-bit accesses; arithmetic is fp32 with
+// the same rounding points as the torch reference ops.
+#include <float.h>
+
+#include "common.cuh"
+
+namespace b200mops {
+namespace {
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------- siluAndMul
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kThreads)
+silu_mul_kernel(const T* __restrict__ x, const T* __restrict__ y, int64_t rows, int n,
+                int64_t x_stride0, int64_t y_stride0, T* __restrict__ out) {
+    constexpr int E = kVec ? Vec16<T>::kElems : 1;
+    const int per_row = n / E;
+    const int64_t idx = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (idx >= rows * per_row) return;
+    const int64_t r = idx / per_row;
+    const int c = (int)(idx - r * per_row) * E;
+    auto f = [](T xv, T yv) {
+        const float a = DType<T>::to_f32(xv);
+        const T act = DType<T>::from_f32(__fdiv_rn(a, 1.f + expf(-a)));
+        return DType<T>::from_f32(DType<T>::to_f32(act) * DType<T>::to_f32(yv));
+    };
+    if (kVec) {
+        const Vec16<T> xv = load16_stream(x + r * x_stride0 + c);
+        const Vec16<T> yv = load16_stream(y + r * y_stride0 + c);
+        Vec16<T> ov;
+#pragma unroll
+        for (int e = 0; e < Vec16<T>::kElems; ++e) ov.v[e] = f(xv.v[e], yv.v[e]);
+        store16(out + r * (int64_t)n + c, ov);
+    } else {
+        out[r * (int64_t)n + c] = f(x[r * x_stride0 + c], y[r * y_stride0 + c]);
+    }
+}
+
+// ---------------------------------------------------------------- rotary
+// One thread rotates E matching elements of the two halves of one head.
+template <typename T, bool kVec>
+__global__ void __launch_bounds__(kThreads)
+rope_neox_kernel(const T* __restrict__ x, int64_t tokens, int heads, int half,
+                 int64_t x_stride0, int64_t x_stride1,
+                 const float* __restrict__ cos, const float* __restrict__ sin, int64_t cs_stride0,
+                 T* __restrict__ out) {
+    constexpr int E = kVec ? Vec16<T>::kElems : 1;
+    const int per_head = half / E;
+    const int64_t idx = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (idx >= tokens * heads * per_head) return;
+    const int64_t th = idx / per_head;
+    const int c = (int)(idx - th * per_head) * E;
+    const int64_t t = th / heads;
+    const int h = (int)(th - t * heads);
+    const T* xp = x + t * x_stride0 + h * x_stride1 + c;
+    T* op = out + th * (int64_t)(2 * half) + c;
+    const float* cp = cos + t * cs_stride0 + c;
+    const float* sp = sin + t * cs_stride0 + c;
+    // No fused multiply-add here: the reference evaluates x1*cos, x2*sin and the
+    // subtraction as separately rounded fp32 operations.
+    if (kVec) {
+        const Vec16<T> x1 = load16_stream(xp), x2 = load16_stream(xp + half);
+        Vec16<T> y1, y2;
+#pragma unroll
+        for (int e = 0; e < Vec16<T>::kElems; ++e) {
+            const float a = DType<T>::to_f32(x1.v[e]), b = DType<T>::to_f32(x2.v[e]);
+            const float cs = __ldg(cp + e), sn = __ldg(sp + e);
+            y1.v[e] = DType<T>::from_f32(__fsub_rn(__fmul_rn(a, cs), __fmul_rn(b, sn)));
+            y2.v[e] = DType<T>::from_f32(__fadd_rn(__fmul_rn(b, cs), __fmul_rn(a, sn)));
+        }
+        store16(op, y1);
+        store16(op + half, y2);
+    } else {
+        const float a = DType<T>::to_f32(xp[0]), b = DType<T>::to_f32(xp[half]);
+        const float cs = cp[0], sn = sp[0];
+        op[0] = DType<T>::from_f32(__fsub_rn(__fmul_rn(a, cs), __fmul_rn(b, sn)));
+        op[half] = DType<T>::from_f32(__fadd_rn(__fmul_rn(b, cs), __fmul_rn(a, sn)));
+    }
+}
+
+// ---------------------------------------------------------------- argmax sampling
+struct Best {
+    float val;
+    int idx;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+    // Larger value wins; equal values keep the lower index.
+    if (b.val > a.val || (b.val == a.val && b.idx < a.idx)) return b;
+    return a;
+}
+__device__ __forceinline__ Best block_best(Best b, Best* smem) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, b.val, o), __shfl_xor_sync(0xffffffffu, b.idx, o)};
+        b = better(b, other);
+    }
+    if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = b;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        b = threadIdx.x < kThreads / 32 ? smem[threadIdx.x] : Best{-FLT_MAX, INT32_MAX};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other{__shfl_xor_sync(0xffffffffu, b.val, o), __shfl_xor_sync(0xffffffffu, b.idx, o)};
+            b = better(b, other);
+        }
+    }
+    return b;  // valid in thread 0
+}
+
+constexpr int kMaxSplits = 64;
+
+// grid (splits, rows): block (s, r) scans columns [s*span, (s+1)*span) of row r.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+argmax_partial_kernel(const T* __restrict__ logits, int vocab, int64_t stride0,
+                      const float* __restrict__ temperatures, int span,
+                      Best* __restrict__ partial, int64_t* __restrict__ out) {
+    __shared__ Best smem[kThreads / 32];
+    constexpr int E = Vec16<T>::kElems;
+    const int r = blockIdx.y, s = blockIdx.x;
+    const T* row = logits + (int64_t)r * stride0;
+    const float temp = __ldg(temperatures + r);
+    const int begin = s * span, end = min(vocab, begin + span);
+    Best b{-FLT_MAX, INT32_MAX};
+    const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) && (begin % E == 0);
+    int scalar_from = begin;  // columns [scalar_from, end) are read one element at a time
+    if (vec && end > begin) {
+        const int n_full = (end - begin) / E;
+        for (int i = threadIdx.x; i < n_full; i += kThreads) {
+            const int c = begin + i * E;
+            const Vec16<T> v = load16_stream(row + c);
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+                b = better(b, Best{__fdiv_rn(DType<T>::to_f32(v.v[e]), temp), c + e});
+        }
+        scalar_from = begin + n_full * E;
+    }
+    for (int c = scalar_from + threadIdx.x; c < end; c += kThreads)
+        b = better(b, Best{__fdiv_rn(DType<T>::to_f32(row[c]), temp), c});
+    b = block_best(b, smem);
+    if (threadIdx.x == 0) {
+        if (gridDim.x == 1) out[r] = b.idx == INT32_MAX ? 0 : b.idx;
+        else partial[(int64_t)r * gridDim.x + s] = b;
+    }
+}
+
+__global__ void __launch_bounds__(32)
+argmax_final_kernel(const Best* __restrict__ partial, int splits, int64_t* __restrict__ out) {
+    const int r = blockIdx.x;
+    Best b{-FLT_MAX, INT32_MAX};
+    for (int s = threadIdx.x; s < splits; s += 32) b = better(b, partial[(int64_t)r * splits + s]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, b.val, o), __shfl_xor_sync(0xffffffffu, b.idx, o)};
+        b = better(b, other);
+    }
+    if (threadIdx.x == 0) out[r] = b.idx == INT32_MAX ? 0 : b.idx;
+}
+
+int argmax_splits(int64_t rows, int64_t vocab) {
+    if (rows <= 0) return 1;
+    int64_t s = (2 * kNumSMs + rows - 1) / rows;
+    const int64_t max_by_vocab = (vocab + 4095) / 4096;  // at least ~4k columns per block
+    if (s > max_by_vocab) s = max_by_vocab;
+    if (s > kMaxSplits) s = kMaxSplits;
+    if (s < 1) s = 1;
+    return (int)s;
+}
+
+}  // namespace
+}  // namespace b200mops
+
+using namespace b200mops;
+
+extern "C" int b200mops_silu_mul(const void* x, const void* y, int64_t rows, int64_t n,
+                                 int64_t x_stride0, int64_t y_stride0, void* out,
+                                 int dtype, void* stream) {
+    if (rows < 0 || n <= 0 || n > INT32_MAX) return B200MOPS_ERR_SHAPE;
+    if (rows == 0) return B200MOPS_OK;
+    if (!x || !y || !out) return B200MOPS_ERR_NULL_POINTER;
+    if (x_stride0 < n || y_stride0 < n) return B200MOPS_ERR_STRIDE;
+    B200MOPS_DISPATCH_DTYPE(dtype, {
+        constexpr int E = Vec16<T>::kElems;
+        const bool vec = n % E == 0 && x_stride0 % E == 0 && y_stride0 % E == 0 &&
+                         aligned16(x) && aligned16(y) && aligned16(out);
+        const int64_t work = rows * (vec ? n / E : n);
+        const unsigned blocks = (unsigned)((work + kThreads - 1) / kThreads);
+        if (vec) silu_mul_kernel<T, true><<<blocks, kThreads, 0, as_stream(stream)>>>(
+            (const T*)x, (const T*)y, rows, (int)n, x_stride0, y_stride0, (T*)out);
+        else silu_mul_kernel<T, false><<<blocks, kThreads, 0, as_stream(stream)>>>(
+            (const T*)x, (const T*)y, rows, (int)n, x_stride0, y_stride0, (T*)out);
+    });
+    return launch_status();
+}
+
+extern "C" int b200mops_rope_neox(const void* x, int64_t tokens, int64_t heads, int64_t head_dim,
+                                  int64_t x_stride0, int64_t x_stride1,
+                                  const float* cos, const float* sin, int64_t cs_stride0,
+                                  void* out, int dtype, void* stream) {
+    if (tokens < 0 || heads <= 0 || head_dim <= 0 || (head_dim & 1) || heads > INT32_MAX ||
+        head_dim > INT32_MAX)
+        return B200MOPS_ERR_SHAPE;
+    if (tokens == 0) return B200MOPS_OK;
+    if (!x || !cos || !sin || !out) return B200MOPS_ERR_NULL_POINTER;
+    if (x_stride1 < head_dim || x_stride0 < 0 || cs_stride0 < 0) return B200MOPS_ERR_STRIDE;
+    const int half = (int)(head_dim / 2);
+    B200MOPS_DISPATCH_DTYPE(dtype, {
+        constexpr int E = Vec16<T>::kElems;
+        const bool vec = half % E == 0 && x_stride0 % E == 0 && x_stride1 % E == 0 &&
+                         aligned16(x) && aligned16(out);
+        const int64_t work = tokens * heads * (vec ? half / E : half);
+        const unsigned blocks = (unsigned)((work + kThreads - 1) / kThreads);
+        if (vec) rope_neox_kernel<T, true><<<blocks, kThreads, 0, as_stream(stream)>>>(
+            (const T*)x, tokens, (int)heads, half, x_stride0, x_stride1, cos, sin, cs_stride0, (T*)out);
+        else rope_neox_kernel<T, false><<<blocks, kThreads, 0, as_stream(stream)>>>(
+            (const T*)x, tokens, (int)heads, half, x_stride0, x_stride1, cos, sin, cs_stride0, (T*)out);
+    });
+    return launch_status();
+}
+
+extern "C" size_t b200mops_sample_argmax_workspace_bytes(int64_t rows, int64_t vocab) {
+    if (rows <= 0) return 0;
+    return (size_t)rows * (size_t)argmax_splits(rows, vocab) * sizeof(Best);
+}
+
+extern "C" int b200mops_sample_argmax(const void* logits, int64_t rows, int64_t vocab,
+                                      int64_t stride0, const float* temperatures, int64_t* out,
+                                      void* workspace, size_t workspace_bytes,
+                                      int dtype, void* stream) {
+    if (rows < 0 || vocab <= 0 || vocab > INT32_MAX - 64 || rows > 65535) return B200MOPS_ERR_SHAPE;
+    if (rows == 0) return B200MOPS_OK;
+    if (!logits || !temperatures || !out) return B200MOPS_ERR_NULL_POINTER;
+    if (stride0 < vocab) return B200MOPS_ERR_STRIDE;
+    const int splits = argmax_splits(rows, vocab);
+    if (splits > 1 && (!workspace || workspace_bytes < (size_t)rows * splits * sizeof(Best)))
+        return B200MOPS_ERR_WORKSPACE;
+    B200MOPS_DISPATCH_DTYPE(dtype, {
+        constexpr int E = Vec16<T>::kElems;
+        int span = (int)((vocab + splits - 1) / splits);
+        span = (span + E - 1) / E * E;  // keep every block's first column vector-aligned
+        argmax_partial_kernel<T><<<dim3(splits, (unsigned)rows), kThreads, 0, as_stream(stream)>>>(
+            (const T*)logits, (int)vocab, stride0, temperatures, span, (Best*)workspace, out);
+    });
+    if (cudaGetLastError() != cudaSuccess) return B200MOPS_ERR_LAUNCH;
+    if (splits > 1)
+        argmax_final_kernel<<<(unsigned)rows, 32, 0, as_stream(stream)>>>((const Best*)workspace,
+                                                                           splits, out);
+    return launch_status();
+}

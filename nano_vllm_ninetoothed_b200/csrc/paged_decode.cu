@@ -1,0 +1,474 @@
+// Paged decode attention (one query token per sequence) for sm_100a.
+//
+// HBM-bound: every K/V byte of the live context is read exactly once, all G = hq/hkv query
+// heads of a KV head are served from that one read, and nothing is materialised.
+//
+//   grid  (hkv, nsplit, batch): CTA (h, s, b) owns tokens [s*chunk, min(len_b, (s+1)*chunk))
+//         of sequence b for KV head h (split-K over the context length).
+//   block 4 consumer warps + 1 producer warp.
+//   producer: one thread walks the chunk in 64-token tiles, looks the page up in the block
+//         table and issues four TMA loads per tile (K and V, two 64-column halves each) from
+//         the 4-D tensor map [head_dim, hkv, page, num_blocks] into a ring of 128-byte-
+//         swizzled shared-memory stages; completion is counted in bytes on an mbarrier.
+//   consumers: warp w takes tokens [16w, 16w+16) of each tile: S = Q K^T with mma.sync
+//         (the G query heads are rows of a zero-padded 16-row A operand kept in registers),
+//         online softmax in fp32 with quad shuffles, O += P V, then frees the stage.
+//   epilogue: the four warps' (m, l, O) are merged through shared memory; with one split the
+//         normalised row goes straight to `out`, otherwise the un-normalised partial goes to
+//         the workspace and a small combine kernel finishes the row.
+//
+// Tokens past len_b inside the last tile are masked to -inf and their V rows are zeroed in
+// shared memory first, so stale or non-finite bytes in unused slots never reach the output.
+// Block-table entries are read only for pages that hold live tokens.
+#include <math.h>
+
+#include "attn_common.cuh"
+
+namespace b200mops {
+namespace {
+
+constexpr int kTile = 64;                 // tokens per pipeline stage
+constexpr int kHeadDim = 128;
+constexpr int kConsumerWarps = 4;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kHalfBytes = kTile * 128;   // one [64 x 64] 16-bit swizzled tile
+constexpr int kStageBytes = 4 * kHalfBytes;  // K lo, K hi, V lo, V hi
+constexpr int kMaxChunkPages = 128;       // page ids staged in shared memory per CTA
+constexpr int kMergeStride = kHeadDim + 4;   // padded row of the cross-warp merge buffer
+constexpr int kMaxGroup = 16;
+
+struct DecodeParams {
+    const void* q; int64_t q_stride_b, q_stride_h;
+    void* out; int64_t out_stride_b, out_stride_h;
+    const int32_t* lens;
+    const int32_t* table; int64_t table_stride;
+    int hq, group, page, num_blocks, chunk, nsplit;
+    float scale_log2;
+    float* ws_o;    // [batch, hq, nsplit, 128] un-normalised partial outputs
+    float* ws_ml;   // [batch, hq, nsplit, 2]   running max (log2 domain) and sum
+    int32_t* status;
+};
+
+template <int kStages>
+constexpr int decode_smem_bytes() {
+    // 1 KB slack for manual 1024-byte alignment of the stage ring.
+    return 1024 + kStages * kStageBytes + 2 * kStages * 8 +
+           kConsumerWarps * kMaxGroup * 2 * 4 + kMaxChunkPages * 4;
+}
+
+__device__ __forceinline__ void consumer_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+
+template <typename T, int kStages>
+__global__ void __launch_bounds__(kThreads, 2)
+paged_decode_kernel(const __grid_constant__ CUtensorMap tm_k,
+                    const __grid_constant__ CUtensorMap tm_v, const DecodeParams p) {
+    static_assert(kStages * kStageBytes >= kConsumerWarps * kMaxGroup * kMergeStride * 4,
+                  "merge buffer must fit in the stage ring");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* empty_bar = full_bar + kStages;
+    float* ml_buf = reinterpret_cast<float*>(empty_bar + kStages);   // [warps][16][2]
+    int32_t* page_ids = reinterpret_cast<int32_t*>(ml_buf + kConsumerWarps * kMaxGroup * 2);
+
+    const int h = blockIdx.x, split = blockIdx.y, b = blockIdx.z;
+    const int G = p.group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int len = __ldg(p.lens + b);
+    const int c0 = split * p.chunk;
+    if (c0 >= len) {
+        // An empty sequence still owes its output rows when no combine pass follows.
+        if (split == 0 && p.nsplit == 1) {
+            T* ob = reinterpret_cast<T*>(p.out) + (int64_t)b * p.out_stride_b +
+                    (int64_t)h * G * p.out_stride_h;
+            for (int i = threadIdx.x; i < G * kHeadDim; i += kThreads)
+                ob[(int64_t)(i / kHeadDim) * p.out_stride_h + (i % kHeadDim)] = DType<T>::from_f32(0.f);
+        }
+        return;
+    }
+    const int c1 = min(len, c0 + p.chunk);
+    const int ntiles = (c1 - c0 + kTile - 1) / kTile;
+    const uint32_t stage0 = smem_u32(smem);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(full_bar + s), 1);
+            mbar_init(smem_u32(empty_bar + s), kConsumerWarps);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------ producer warp
+        const int first_page = c0 / p.page;
+        const int npages = (c1 - 1) / p.page - first_page + 1;
+        bool bad = false;
+        for (int j = lane; j < npages; j += 32) {
+            const int id = __ldg(p.table + (int64_t)b * p.table_stride + first_page + j);
+            bad |= (id < 0 || id >= p.num_blocks);
+            page_ids[j] = id;   // an out-of-range id makes TMA zero-fill instead of faulting
+        }
+        if (bad && p.status) atomicOr(p.status, B200MOPS_DEV_BAD_PAGE);
+        __syncwarp();
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            for (int i = 0; i < ntiles; ++i) {
+                const int s = i % kStages;
+                const int round = i / kStages;
+                if (round > 0 &&
+                    !mbar_wait(smem_u32(empty_bar + s), (uint32_t)(round - 1) & 1u, p.status))
+                    break;
+                const int tok = c0 + i * kTile;
+                const int pg = tok / p.page;
+                const int in_pg = tok - pg * p.page;
+                const int page_id = page_ids[pg - first_page];
+                const uint32_t bar = smem_u32(full_bar + s);
+                const uint32_t dst = stage0 + s * kStageBytes;
+                mbar_arrive_expect_tx(bar, kStageBytes);
+                tma_load_4d(dst, &tm_k, bar, 0, h, in_pg, page_id);
+                tma_load_4d(dst + kHalfBytes, &tm_k, bar, 64, h, in_pg, page_id);
+                tma_load_4d(dst + 2 * kHalfBytes, &tm_v, bar, 0, h, in_pg, page_id);
+                tma_load_4d(dst + 3 * kHalfBytes, &tm_v, bar, 64, h, in_pg, page_id);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumer warps
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t qa[kHeadDim / 16][4];
+    {
+        const T* qb = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_stride_b +
+                      (int64_t)h * G * p.q_stride_h;
+        const T* r0 = qb + (int64_t)g * p.q_stride_h;
+        const T* r1 = qb + (int64_t)(g + 8) * p.q_stride_h;
+#pragma unroll
+        for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+            const int col = ks * 16 + 2 * t;
+            qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(r0 + col) : 0u;
+            qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(r1 + col) : 0u;
+            qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(r0 + col + 8) : 0u;
+            qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(r1 + col + 8) : 0u;
+        }
+    }
+
+    float o[kHeadDim / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < kHeadDim / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const float c = p.scale_log2;
+    const int mi = lane >> 3, r8 = lane & 7;   // ldmatrix: matrix index and row within it
+
+    for (int i = 0; i < ntiles; ++i) {
+        const int s = i % kStages;
+        const bool ready = mbar_wait(smem_u32(full_bar + s), (uint32_t)(i / kStages) & 1u, p.status);
+        if (!__all_sync(0xffffffffu, ready)) break;
+        const int valid = c1 - (c0 + i * kTile + warp * 16);   // live tokens among this warp's 16
+        if (valid > 0) {
+            const uint32_t k_lo = stage0 + s * kStageBytes;
+            const uint32_t v_lo = k_lo + 2 * kHalfBytes;
+            if (valid < 16) {
+                // Zero the dead V rows: 0 * NaN would otherwise poison the accumulators.
+                for (int idx = lane; idx < (16 - valid) * 16; idx += 32) {
+                    const int row = warp * 16 + valid + (idx >> 4);
+                    const int pk = idx & 15;
+                    const uint32_t a = swz128(v_lo + (pk >> 3) * kHalfBytes, row, pk & 7);
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0u) : "memory");
+                }
+                __syncwarp();
+            }
+            // S[16 q rows x 16 tokens] = Q K^T
+            float sc[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+            {
+                const int row = warp * 16 + (mi >> 1) * 8 + r8;
+#pragma unroll
+                for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+                    const int pk = 2 * ks + (mi & 1);
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(swz128(k_lo + (pk >> 3) * kHalfBytes, row, pk & 7), b0, b1, b2, b3);
+                    mma16816<T>(sc[0], qa[ks], b0, b1);
+                    mma16816<T>(sc[1], qa[ks], b2, b3);
+                }
+            }
+            if (valid < 16) {
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (nt * 8 + 2 * t + (j & 1) >= valid) sc[nt][j] = -INFINITY;
+            }
+            // Online softmax in the log2 domain; rows g and g+8 of the padded query block.
+            float mx0 = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
+            float mx1 = fmaxf(fmaxf(sc[0][2], sc[0][3]), fmaxf(sc[1][2], sc[1][3]));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0 * c), mn1 = fmaxf(m1, mx1 * c);
+            const float corr0 = fast_exp2(m0 - mn0), corr1 = fast_exp2(m1 - mn1);
+            m0 = mn0; m1 = mn1;
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                sc[nt][0] = fast_exp2(fmaf(sc[nt][0], c, -mn0));
+                sc[nt][1] = fast_exp2(fmaf(sc[nt][1], c, -mn0));
+                sc[nt][2] = fast_exp2(fmaf(sc[nt][2], c, -mn1));
+                sc[nt][3] = fast_exp2(fmaf(sc[nt][3], c, -mn1));
+                ps0 += sc[nt][0] + sc[nt][1];
+                ps1 += sc[nt][2] + sc[nt][3];
+            }
+            l0 = fmaf(l0, corr0, ps0);
+            l1 = fmaf(l1, corr1, ps1);
+            if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {
+#pragma unroll
+                for (int nt = 0; nt < kHeadDim / 8; ++nt) {
+                    o[nt][0] *= corr0; o[nt][1] *= corr0;
+                    o[nt][2] *= corr1; o[nt][3] *= corr1;
+                }
+            }
+            uint32_t pa[4];
+            pa[0] = pack2<T>(sc[0][0], sc[0][1]);
+            pa[1] = pack2<T>(sc[0][2], sc[0][3]);
+            pa[2] = pack2<T>(sc[1][0], sc[1][1]);
+            pa[3] = pack2<T>(sc[1][2], sc[1][3]);
+            // O[16 x 128] += P[16 x 16 tokens] V[16 tokens x 128]
+            {
+                const int row = warp * 16 + (mi & 1) * 8 + r8;
+#pragma unroll
+                for (int np = 0; np < kHeadDim / 16; ++np) {
+                    const int pk = 2 * np + (mi >> 1);
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4_trans(swz128(v_lo + (pk >> 3) * kHalfBytes, row, pk & 7), b0, b1, b2, b3);
+                    mma16816<T>(o[2 * np], pa, b0, b1);
+                    mma16816<T>(o[2 * np + 1], pa, b2, b3);
+                }
+            }
+            if (valid < 16) fence_proxy_async_smem();   // our zero fill precedes the next TMA write
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(empty_bar + s));
+    }
+
+    // ---------------------------------------------------------------- merge the four warps
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    float* obuf = reinterpret_cast<float*>(smem);   // [warps][16][kMergeStride], reuses the ring
+    consumer_sync();   // every warp has finished reading the stages
+    {
+        float* wb = obuf + warp * kMaxGroup * kMergeStride;
+        if (g < G) {
+#pragma unroll
+            for (int nt = 0; nt < kHeadDim / 8; ++nt)
+                *reinterpret_cast<float2*>(wb + g * kMergeStride + nt * 8 + 2 * t) =
+                    make_float2(o[nt][0], o[nt][1]);
+            if (t == 0) {
+                ml_buf[(warp * kMaxGroup + g) * 2] = m0;
+                ml_buf[(warp * kMaxGroup + g) * 2 + 1] = l0;
+            }
+        }
+        if (g + 8 < G) {
+#pragma unroll
+            for (int nt = 0; nt < kHeadDim / 8; ++nt)
+                *reinterpret_cast<float2*>(wb + (g + 8) * kMergeStride + nt * 8 + 2 * t) =
+                    make_float2(o[nt][2], o[nt][3]);
+            if (t == 0) {
+                ml_buf[(warp * kMaxGroup + g + 8) * 2] = m1;
+                ml_buf[(warp * kMaxGroup + g + 8) * 2 + 1] = l1;
+            }
+        }
+    }
+    consumer_sync();
+    const int d = threadIdx.x;   // 0..127: one output column per consumer thread
+    for (int r = 0; r < G; ++r) {
+        float mw[kConsumerWarps], M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+            mw[w] = ml_buf[(w * kMaxGroup + r) * 2];
+            M = fmaxf(M, mw[w]);
+        }
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; ++w) {
+            const float f = fast_exp2(mw[w] - M);   // a warp that saw no token has m = -inf -> 0
+            acc = fmaf(f, obuf[(w * kMaxGroup + r) * kMergeStride + d], acc);
+            L = fmaf(f, ml_buf[(w * kMaxGroup + r) * 2 + 1], L);
+        }
+        const int hq_idx = h * G + r;
+        if (p.nsplit == 1) {
+            T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.out_stride_b +
+                      (int64_t)hq_idx * p.out_stride_h;
+            orow[d] = DType<T>::from_f32(acc / L);
+        } else {
+            const int64_t slot = ((int64_t)b * p.hq + hq_idx) * p.nsplit + split;
+            p.ws_o[slot * kHeadDim + d] = acc;
+            if (d == 0) {
+                p.ws_ml[slot * 2] = M;
+                p.ws_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// grid (hq, batch), 128 threads: fold the live splits of one output row.
+template <typename T>
+__global__ void __launch_bounds__(kHeadDim)
+paged_decode_combine_kernel(const DecodeParams p) {
+    const int hq_idx = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const int len = __ldg(p.lens + b);
+    const int live = len <= 0 ? 0 : min(p.nsplit, (len + p.chunk - 1) / p.chunk);
+    const int64_t base = ((int64_t)b * p.hq + hq_idx) * p.nsplit;
+    float M = -INFINITY;
+    for (int s = 0; s < live; ++s) M = fmaxf(M, __ldg(p.ws_ml + (base + s) * 2));
+    float acc = 0.f, L = 0.f;
+    for (int s = 0; s < live; ++s) {
+        const float f = fast_exp2(__ldg(p.ws_ml + (base + s) * 2) - M);
+        acc = fmaf(f, __ldg(p.ws_o + (base + s) * kHeadDim + d), acc);
+        L = fmaf(f, __ldg(p.ws_ml + (base + s) * 2 + 1), L);
+    }
+    T* orow = reinterpret_cast<T*>(p.out) + (int64_t)b * p.out_stride_b +
+              (int64_t)hq_idx * p.out_stride_h;
+    orow[d] = DType<T>::from_f32(live ? acc / L : 0.f);
+}
+
+int round_up(int64_t v, int m) { return (int)((v + m - 1) / m * m); }
+
+int auto_chunk(int64_t batch, int64_t hkv, int64_t page, int64_t max_blocks) {
+    const int64_t max_len = max_blocks * page;
+    // Aim for several CTAs per resident slot (2 per SM) even when the real lengths are
+    // half the table width, but keep a chunk long enough to amortise pipeline fill.
+    const int64_t target_ctas = (int64_t)kNumSMs * 2 * 4;
+    int64_t chunk = (batch * hkv * max_len + target_ctas - 1) / target_ctas;
+    if (chunk < 128) chunk = 128;
+    if (chunk > 1024) chunk = 1024;
+    chunk = round_up(chunk, kTile);
+    if (chunk >= max_len) chunk = round_up(max_len, kTile);
+    return (int)chunk;
+}
+
+int clamp_chunk(int chunk, int64_t page, int64_t max_blocks) {
+    chunk = round_up(chunk < kTile ? kTile : chunk, kTile);
+    const int64_t max_len = max_blocks * page;
+    if (chunk > max_len) chunk = round_up(max_len, kTile);
+    const int64_t cap = (int64_t)(kMaxChunkPages - 1) * page;   // page ids staged per CTA
+    if (chunk > cap) chunk = (int)(cap / kTile * kTile);
+    return chunk;
+}
+
+template <typename T, int kStages>
+int launch_decode(const CUtensorMap& tm_k, const CUtensorMap& tm_v, const DecodeParams& p,
+                  int64_t batch, int64_t hkv, cudaStream_t st) {
+    constexpr int smem = decode_smem_bytes<kStages>();
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(paged_decode_kernel<T, kStages>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return B200MOPS_ERR_LAUNCH;
+        configured = true;
+    }
+    paged_decode_kernel<T, kStages><<<dim3((unsigned)hkv, (unsigned)p.nsplit, (unsigned)batch),
+                                      kThreads, smem, st>>>(tm_k, tm_v, p);
+    if (cudaGetLastError() != cudaSuccess) return B200MOPS_ERR_LAUNCH;
+    if (p.nsplit > 1) {
+        paged_decode_combine_kernel<T><<<dim3((unsigned)p.hq, (unsigned)batch), kHeadDim, 0, st>>>(p);
+        if (cudaGetLastError() != cudaSuccess) return B200MOPS_ERR_LAUNCH;
+    }
+    return B200MOPS_OK;
+}
+
+}  // namespace
+}  // namespace b200mops
+
+using namespace b200mops;
+
+extern "C" int32_t b200mops_paged_decode_auto_chunk(int64_t batch, int64_t hkv, int64_t page,
+                                                    int64_t max_blocks_per_seq) {
+    if (batch <= 0 || hkv <= 0 || page <= 0 || max_blocks_per_seq <= 0) return kTile;
+    return clamp_chunk(auto_chunk(batch, hkv, page, max_blocks_per_seq), page, max_blocks_per_seq);
+}
+
+extern "C" size_t b200mops_paged_decode_workspace_bytes(int64_t batch, int64_t hq, int64_t hkv,
+                                                        int64_t head_dim, int64_t page,
+                                                        int64_t max_blocks_per_seq,
+                                                        int32_t chunk_tokens) {
+    if (batch <= 0 || hq <= 0 || hkv <= 0 || page <= 0 || max_blocks_per_seq <= 0) return 0;
+    const int chunk = chunk_tokens > 0 ? clamp_chunk(chunk_tokens, page, max_blocks_per_seq)
+                                       : b200mops_paged_decode_auto_chunk(batch, hkv, page, max_blocks_per_seq);
+    const int64_t nsplit = (max_blocks_per_seq * page + chunk - 1) / chunk;
+    if (nsplit <= 1) return 0;
+    return (size_t)(batch * hq * nsplit) * (size_t)(head_dim + 2) * sizeof(float);
+}
+
+extern "C" int b200mops_paged_decode(const b200mops_paged_decode_args* a, void* stream) {
+    if (!a) return B200MOPS_ERR_NULL_POINTER;
+    if (a->dtype != B200MOPS_BF16 && a->dtype != B200MOPS_F16) return B200MOPS_ERR_DTYPE;
+    if (a->batch < 0 || a->hq <= 0 || a->hkv <= 0 || a->num_blocks <= 0 || a->page <= 0 ||
+        a->max_blocks_per_seq <= 0 || a->batch > 65535 || a->hkv > 65535 ||
+        a->num_blocks > INT32_MAX || a->page > INT32_MAX)
+        return B200MOPS_ERR_SHAPE;
+    if (a->batch == 0) return B200MOPS_OK;
+    if (a->head_dim != kHeadDim) return B200MOPS_ERR_HEAD_DIM;
+    if (a->hq % a->hkv != 0 || a->hq / a->hkv > kMaxGroup) return B200MOPS_ERR_GQA;
+    if (a->page % kTile != 0) return B200MOPS_ERR_PAGE_SIZE;
+    if (!a->q || !a->out || !a->k_cache || !a->v_cache || !a->cache_seqlens || !a->block_table)
+        return B200MOPS_ERR_NULL_POINTER;
+    if (!(a->softmax_scale > 0.f)) return B200MOPS_ERR_UNSUPPORTED;
+    if (a->table_stride0 < a->max_blocks_per_seq || a->q_stride_h < kHeadDim ||
+        a->out_stride_h < kHeadDim)
+        return B200MOPS_ERR_STRIDE;
+    // Query rows are read as 32-bit pairs.
+    if ((reinterpret_cast<uintptr_t>(a->q) & 3u) || (a->q_stride_b & 1) || (a->q_stride_h & 1))
+        return B200MOPS_ERR_ALIGNMENT;
+
+    const int chunk = a->chunk_tokens > 0
+                          ? clamp_chunk(a->chunk_tokens, a->page, a->max_blocks_per_seq)
+                          : b200mops_paged_decode_auto_chunk(a->batch, a->hkv, a->page,
+                                                             a->max_blocks_per_seq);
+    const int64_t nsplit = (a->max_blocks_per_seq * a->page + chunk - 1) / chunk;
+    if (nsplit > 65535) return B200MOPS_ERR_TOO_LARGE;
+    const size_t need = nsplit > 1 ? (size_t)(a->batch * a->hq * nsplit) * (kHeadDim + 2) * sizeof(float) : 0;
+    if (need && (!a->workspace || a->workspace_bytes < need || !aligned16(a->workspace)))
+        return B200MOPS_ERR_WORKSPACE;
+
+    CUtensorMap tm_k, tm_v;
+    const uint64_t dims[4] = {(uint64_t)kHeadDim, (uint64_t)a->hkv, (uint64_t)a->page,
+                              (uint64_t)a->num_blocks};
+    const uint32_t box[4] = {64, 1, (uint32_t)kTile, 1};
+    const uint64_t ks[3] = {(uint64_t)a->k_stride_head * 2, (uint64_t)a->k_stride_token * 2,
+                            (uint64_t)a->k_stride_block * 2};
+    const uint64_t vs[3] = {(uint64_t)a->v_stride_head * 2, (uint64_t)a->v_stride_token * 2,
+                            (uint64_t)a->v_stride_block * 2};
+    if (a->k_stride_head < kHeadDim || a->v_stride_head < kHeadDim || a->k_stride_token <= 0 ||
+        a->v_stride_token <= 0 || a->k_stride_block <= 0 || a->v_stride_block <= 0)
+        return B200MOPS_ERR_STRIDE;
+    int rc = encode_map_16bit(&tm_k, a->dtype, a->k_cache, 4, dims, ks, box);
+    if (rc != B200MOPS_OK) return rc;
+    rc = encode_map_16bit(&tm_v, a->dtype, a->v_cache, 4, dims, vs, box);
+    if (rc != B200MOPS_OK) return rc;
+
+    DecodeParams p;
+    p.q = a->q; p.q_stride_b = a->q_stride_b; p.q_stride_h = a->q_stride_h;
+    p.out = a->out; p.out_stride_b = a->out_stride_b; p.out_stride_h = a->out_stride_h;
+    p.lens = a->cache_seqlens;
+    p.table = a->block_table; p.table_stride = a->table_stride0;
+    p.hq = (int)a->hq; p.group = (int)(a->hq / a->hkv);
+    p.page = (int)a->page; p.num_blocks = (int)a->num_blocks;
+    p.chunk = chunk; p.nsplit = (int)nsplit;
+    p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+    p.ws_o = reinterpret_cast<float*>(a->workspace);
+    p.ws_ml = p.ws_o ? p.ws_o + (size_t)(a->batch * a->hq * nsplit) * kHeadDim : nullptr;
+    p.status = a->status_word;
+    cudaStream_t st = as_stream(stream);
+    if (a->dtype == B200MOPS_BF16)
+        return launch_decode<__nv_bfloat16, 3>(tm_k, tm_v, p, a->batch, a->hkv, st);
+    return launch_decode<__half, 3>(tm_k, tm_v, p, a->batch, a->hkv, st);
+}

@@ -1,0 +1,211 @@
+// rms_forward and add_rms_forward (fused residual add + RMSNorm).
+// HBM-bound row kernels: a group of 8/16/32 lanes keeps one whole row in registers
+// (128-bit loads issued back to back), reduces the sum of squares with shuffles,
+// then writes the normalised row -- every byte crosses HBM exactly once.
+// Rounding follows the torch reference op for op:
+//   s = f32(x) (+ f32(r));  res_out = cast(s);  out = cast(f32(cast(s * rstd)) * f32(w))
+// with the variance taken from the unrounded fp32 s.
+#include "common.cuh"
+
+namespace b200mops {
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float inv_rms(float sumsq, float n, float eps) {
+    // 1/sqrt with IEEE rounding of both steps, as torch.rsqrt on the host computes it.
+    return __frcp_rn(__fsqrt_rn(__fdiv_rn(sumsq, n) + eps));
+}
+
+// Row r = (i0, i1) lives at x + i0*stride0 + i1*stride1.  kAdd fuses the residual add.
+template <typename T, int kMaxVpl, bool kAdd>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_group_kernel(const T* __restrict__ x, const T* __restrict__ residual,
+                     int64_t rows, int64_t rows1, int64_t x_stride0, int64_t x_stride1,
+                     int64_t res_stride0, const T* __restrict__ weight, float eps,
+                     T* __restrict__ out, T* __restrict__ res_out,
+                     int n, int group, int vpl) {
+    constexpr int E = Vec16<T>::kElems;
+    const int lane = threadIdx.x & 31;
+    const int lig = lane & (group - 1);
+    const int rows_per_warp = 32 / group;
+    const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    const int64_t row = warp * rows_per_warp + lane / group;
+    const bool active = row < rows;
+
+    float s[kMaxVpl][E];
+    float sumsq = 0.f;
+    if (active) {
+        const int64_t i0 = row / rows1, i1 = row - i0 * rows1;
+        const T* xr = x + i0 * x_stride0 + i1 * x_stride1;
+        Vec16<T> xv[kMaxVpl];
+#pragma unroll
+        for (int v = 0; v < kMaxVpl; ++v)
+            if (v < vpl) xv[v] = load16_stream(xr + (int64_t)(v * group + lig) * E);
+        if (kAdd) {
+            const T* rr = residual + row * res_stride0;
+            Vec16<T> rv[kMaxVpl];
+#pragma unroll
+            for (int v = 0; v < kMaxVpl; ++v)
+                if (v < vpl) rv[v] = load16_stream(rr + (int64_t)(v * group + lig) * E);
+#pragma unroll
+            for (int v = 0; v < kMaxVpl; ++v)
+                if (v < vpl) {
+                    Vec16<T> ro;
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        s[v][e] = DType<T>::to_f32(xv[v].v[e]) + DType<T>::to_f32(rv[v].v[e]);
+                        ro.v[e] = DType<T>::from_f32(s[v][e]);
+                    }
+                    store16(res_out + row * (int64_t)n + (int64_t)(v * group + lig) * E, ro);
+                }
+        } else {
+#pragma unroll
+            for (int v = 0; v < kMaxVpl; ++v)
+                if (v < vpl) {
+#pragma unroll
+                    for (int e = 0; e < E; ++e) s[v][e] = DType<T>::to_f32(xv[v].v[e]);
+                }
+        }
+#pragma unroll
+        for (int v = 0; v < kMaxVpl; ++v)
+            if (v < vpl) {
+#pragma unroll
+                for (int e = 0; e < E; ++e) sumsq = fmaf(s[v][e], s[v][e], sumsq);
+            }
+    }
+    for (int o = group >> 1; o > 0; o >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
+    if (!active) return;
+    const float rstd = inv_rms(sumsq, (float)n, eps);
+#pragma unroll
+    for (int v = 0; v < kMaxVpl; ++v)
+        if (v < vpl) {
+            const int64_t col = (int64_t)(v * group + lig) * E;
+            const Vec16<T> wv = load16(weight + col);
+            Vec16<T> ov;
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                const T normed = DType<T>::from_f32(s[v][e] * rstd);
+                ov.v[e] = DType<T>::from_f32(DType<T>::to_f32(normed) * DType<T>::to_f32(wv.v[e]));
+            }
+            store16(out + row * (int64_t)n + col, ov);
+        }
+}
+
+// Any n, any alignment: one block per row, two sweeps over the row (the second one is
+// served by L1/L2).  Nothing is written before the reduction is complete, and each thread
+// rewrites only elements it has read itself, so out/res_out may alias x/residual.
+template <typename T, bool kAdd>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_generic_kernel(const T* __restrict__ x, const T* __restrict__ residual,
+                       int64_t rows1, int64_t x_stride0, int64_t x_stride1, int64_t res_stride0,
+                       const T* __restrict__ weight, float eps,
+                       T* out, T* res_out, int n) {
+    __shared__ float warp_part[kThreads / 32];
+    __shared__ float total;
+    const int64_t row = blockIdx.x;
+    const int64_t i0 = row / rows1, i1 = row - i0 * rows1;
+    const T* xr = x + i0 * x_stride0 + i1 * x_stride1;
+    const T* rr = kAdd ? residual + row * res_stride0 : nullptr;
+    float sumsq = 0.f;
+    for (int c = threadIdx.x; c < n; c += kThreads) {
+        float v = DType<T>::to_f32(xr[c]);
+        if (kAdd) v += DType<T>::to_f32(rr[c]);
+        sumsq = fmaf(v, v, sumsq);
+    }
+    sumsq = warp_sum(sumsq);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = sumsq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < kThreads / 32; ++w) t += warp_part[w];
+        total = t;
+    }
+    __syncthreads();
+    const float rstd = inv_rms(total, (float)n, eps);
+    for (int c = threadIdx.x; c < n; c += kThreads) {
+        float v = DType<T>::to_f32(xr[c]);
+        if (kAdd) {
+            v += DType<T>::to_f32(rr[c]);
+            res_out[row * (int64_t)n + c] = DType<T>::from_f32(v);
+        }
+        const T normed = DType<T>::from_f32(v * rstd);
+        out[row * (int64_t)n + c] =
+            DType<T>::from_f32(DType<T>::to_f32(normed) * DType<T>::to_f32(weight[c]));
+    }
+}
+
+template <typename T, bool kAdd>
+int launch_rmsnorm(const T* x, const T* residual, int64_t rows0, int64_t rows1,
+                   int64_t x_stride0, int64_t x_stride1, int64_t res_stride0,
+                   const T* weight, float eps, T* out, T* res_out, int64_t n, cudaStream_t st) {
+    constexpr int E = Vec16<T>::kElems;
+    const int64_t rows = rows0 * rows1;
+    if (rows == 0) return B200MOPS_OK;
+    if (n > INT32_MAX || rows > INT32_MAX) return B200MOPS_ERR_TOO_LARGE;
+    bool vec = (n % E == 0) && aligned16(x) && aligned16(out) && aligned16(weight) &&
+               (x_stride0 % E == 0) && (x_stride1 % E == 0);
+    if (kAdd) vec = vec && aligned16(residual) && aligned16(res_out) && (res_stride0 % E == 0);
+    // The register path must not write `out` over rows of x that another group still has to
+    // read; with out == x (same row addressing) every group rewrites only its own row.
+    int group = 0, vpl = 0;
+    if (vec) {
+        const int64_t n_vecs = n / E;
+        if (n_vecs % 32 == 0 && n_vecs >= 64) group = 32;
+        else if (n_vecs % 16 == 0 && n_vecs >= 32) group = 16;
+        else if (n_vecs % 8 == 0) group = 8;
+        if (group) vpl = (int)(n_vecs / group);
+        if (vpl > 16) group = 0;
+    }
+    if (group == 0) {
+        rmsnorm_generic_kernel<T, kAdd><<<(unsigned)rows, kThreads, 0, st>>>(
+            x, residual, rows1, x_stride0, x_stride1, res_stride0, weight, eps, out, res_out, (int)n);
+        return launch_status();
+    }
+    const int rows_per_block = (kThreads / 32) * (32 / group);
+    const unsigned blocks = (unsigned)((rows + rows_per_block - 1) / rows_per_block);
+#define B200MOPS_LAUNCH_GROUP(MAXVPL)                                                        \
+    rmsnorm_group_kernel<T, MAXVPL, kAdd><<<blocks, kThreads, 0, st>>>(                      \
+        x, residual, rows, rows1, x_stride0, x_stride1, res_stride0, weight, eps, out,       \
+        res_out, (int)n, group, vpl)
+    if (vpl <= 2) B200MOPS_LAUNCH_GROUP(2);
+    else if (vpl <= 4) B200MOPS_LAUNCH_GROUP(4);
+    else if (vpl <= 8) B200MOPS_LAUNCH_GROUP(8);
+    else B200MOPS_LAUNCH_GROUP(16);
+#undef B200MOPS_LAUNCH_GROUP
+    return launch_status();
+}
+
+}  // namespace
+}  // namespace b200mops
+
+using namespace b200mops;
+
+extern "C" int b200mops_rmsnorm(const void* x, int64_t rows0, int64_t rows1,
+                                int64_t x_stride0, int64_t x_stride1,
+                                const void* weight, float eps, void* out, int64_t n,
+                                int dtype, void* stream) {
+    if (rows0 < 0 || rows1 < 0 || n <= 0) return B200MOPS_ERR_SHAPE;
+    if (rows0 * rows1 == 0) return B200MOPS_OK;
+    if (!x || !weight || !out) return B200MOPS_ERR_NULL_POINTER;
+    if (x_stride0 < 0 || x_stride1 < 0) return B200MOPS_ERR_STRIDE;
+    B200MOPS_DISPATCH_DTYPE(dtype, return (launch_rmsnorm<T, false>(
+        (const T*)x, nullptr, rows0, rows1, x_stride0, x_stride1, 0, (const T*)weight, eps,
+        (T*)out, nullptr, n, as_stream(stream))));
+    return B200MOPS_ERR_DTYPE;
+}
+
+extern "C" int b200mops_add_rmsnorm(const void* x, const void* residual, int64_t rows, int64_t n,
+                                    int64_t x_stride0, int64_t residual_stride0,
+                                    const void* weight, float eps,
+                                    void* out, void* residual_out,
+                                    int dtype, void* stream) {
+    if (rows < 0 || n <= 0) return B200MOPS_ERR_SHAPE;
+    if (rows == 0) return B200MOPS_OK;
+    if (!x || !residual || !weight || !out || !residual_out) return B200MOPS_ERR_NULL_POINTER;
+    if (x_stride0 < n || residual_stride0 < n) return B200MOPS_ERR_STRIDE;
+    B200MOPS_DISPATCH_DTYPE(dtype, return (launch_rmsnorm<T, true>(
+        (const T*)x, (const T*)residual, rows, 1, x_stride0, 0, residual_stride0,
+        (const T*)weight, eps, (T*)out, (T*)residual_out, n, as_stream(stream))));
+    return B200MOPS_ERR_DTYPE;
+}

@@ -1,0 +1,365 @@
+// Variable-length causal prefill attention for sm_100a, mma.sync edition.
+//
+//   grid  (ceil(max_seqlen_q / 128), hq, batch); CTA = 128 query rows of one head of one
+//         sequence; the heaviest (last) row tiles of a sequence are scheduled first.
+//   block 8 consumer warps (16 query rows each) + 1 producer warp.
+//   producer: TMA-loads the Q tile once, then streams 64-key K/V tiles through a ring of
+//         128-byte-swizzled stages.  K/V come either from the packed [total_k, hkv, 128]
+//         tensors or, with a block table, from the paged caches (one page lookup per tile).
+//   consumers: S = Q K^T and O += P V with mma.sync m16n8k16, fp32 online softmax in
+//         registers, causal tiles above the diagonal skipped, mask aligned bottom-right.
+//
+// This kernel is exact in its handling of ragged shapes and serves every supported
+// configuration; the tcgen05 kernel takes over the shapes it covers.
+#include <math.h>
+
+#include "attn_common.cuh"
+
+namespace b200mops {
+namespace {
+
+constexpr int kBM = 128;                  // query rows per CTA
+constexpr int kBN = 64;                   // keys per stage
+constexpr int kHeadDim = 128;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kHalfBytes = kBN * 128;     // [64 x 64] 16-bit swizzled tile
+constexpr int kStageBytes = 4 * kHalfBytes;
+constexpr int kQBytes = 2 * kBM * 128;    // Q lo + Q hi
+constexpr int kStages = 4;
+constexpr int kSmemBytes = 1024 + kQBytes + kStages * kStageBytes + (2 * kStages + 1) * 8;
+
+struct PrefillParams {
+    void* out; int64_t out_stride_t, out_stride_h;
+    const int32_t* cu_q; const int32_t* cu_k;
+    const int32_t* table; int64_t table_stride;
+    int group, page, num_blocks, causal;
+    float scale_log2;
+    int32_t* status;
+};
+
+__device__ __forceinline__ void consumer_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+varlen_prefill_kernel(const __grid_constant__ CUtensorMap tm_q,
+                      const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~uintptr_t(1023));
+    uint8_t* q_smem = smem;
+    uint8_t* ring = smem + kQBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + kStages * kStageBytes);
+    uint64_t* empty_bar = full_bar + kStages;
+    uint64_t* q_bar = empty_bar + kStages;
+
+    const int hq_idx = blockIdx.y, b = blockIdx.z;
+    const int hk = hq_idx / p.group;
+    const int q_begin = __ldg(p.cu_q + b), len_q = __ldg(p.cu_q + b + 1) - q_begin;
+    const int k_begin = __ldg(p.cu_k + b), len_k = __ldg(p.cu_k + b + 1) - k_begin;
+    const int m_tiles = (len_q + kBM - 1) / kBM;
+    if ((int)blockIdx.x >= m_tiles) return;
+    const int m0 = (m_tiles - 1 - (int)blockIdx.x) * kBM;   // late rows carry the most keys
+    const int off = len_k - len_q;                            // bottom-right causal alignment
+    int n_end = len_k;
+    if (p.causal) n_end = min(len_k, m0 + kBM + off);
+    const int ntiles = n_end > 0 ? (n_end + kBN - 1) / kBN : 0;
+    const bool paged = p.table != nullptr;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(smem_u32(full_bar + s), 1);
+            mbar_init(smem_u32(empty_bar + s), kConsumerWarps);
+        }
+        mbar_init(smem_u32(q_bar), 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == kConsumerWarps) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_q);
+            tma_prefetch_desc(&tm_k);
+            tma_prefetch_desc(&tm_v);
+            const uint32_t qb = smem_u32(q_bar), qd = smem_u32(q_smem);
+            mbar_arrive_expect_tx(qb, kQBytes);
+            tma_load_4d(qd, &tm_q, qb, 0, hq_idx, q_begin + m0, 0);
+            tma_load_4d(qd + kBM * 128, &tm_q, qb, 64, hq_idx, q_begin + m0, 0);
+            for (int i = 0; i < ntiles; ++i) {
+                const int s = i % kStages, round = i / kStages;
+                if (round > 0 &&
+                    !mbar_wait(smem_u32(empty_bar + s), (uint32_t)(round - 1) & 1u, p.status))
+                    break;
+                int c2, c3;
+                if (paged) {
+                    const int tok = i * kBN, pg = tok / p.page;
+                    c3 = __ldg(p.table + (int64_t)b * p.table_stride + pg);
+                    if ((c3 < 0 || c3 >= p.num_blocks) && p.status)
+                        atomicOr(p.status, B200MOPS_DEV_BAD_PAGE);
+                    c2 = tok - pg * p.page;
+                } else {
+                    c2 = k_begin + i * kBN;
+                    c3 = 0;
+                }
+                const uint32_t bar = smem_u32(full_bar + s);
+                const uint32_t dst = smem_u32(ring) + s * kStageBytes;
+                mbar_arrive_expect_tx(bar, kStageBytes);
+                tma_load_4d(dst, &tm_k, bar, 0, hk, c2, c3);
+                tma_load_4d(dst + kHalfBytes, &tm_k, bar, 64, hk, c2, c3);
+                tma_load_4d(dst + 2 * kHalfBytes, &tm_v, bar, 0, hk, c2, c3);
+                tma_load_4d(dst + 3 * kHalfBytes, &tm_v, bar, 64, hk, c2, c3);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+    const int mi = lane >> 3, r8 = lane & 7;
+    const int row_lo = m0 + warp * 16;          // first query row (sequence-local) of this warp
+    uint32_t qa[kHeadDim / 16][4];
+    {
+        const bool ok = mbar_wait(smem_u32(q_bar), 0, p.status);
+        if (!__all_sync(0xffffffffu, ok)) return;
+        const uint32_t qd = smem_u32(q_smem);
+        const int row = warp * 16 + (mi & 1) * 8 + r8;
+#pragma unroll
+        for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+            const int pk = 2 * ks + (mi >> 1);
+            ldsm_x4(swz128(qd + (pk >> 3) * (kBM * 128), row, pk & 7), qa[ks][0], qa[ks][1],
+                    qa[ks][2], qa[ks][3]);
+        }
+    }
+
+    float o[kHeadDim / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < kHeadDim / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    float m0r = -INFINITY, m1r = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const float c = p.scale_log2;
+    // Last visible key (sequence-local) for this thread's two rows.
+    const int lim0 = p.causal ? min(len_k - 1, row_lo + g + off) : len_k - 1;
+    const int lim1 = p.causal ? min(len_k - 1, row_lo + g + 8 + off) : len_k - 1;
+
+    for (int i = 0; i < ntiles; ++i) {
+        const int s = i % kStages;
+        const bool ready = mbar_wait(smem_u32(full_bar + s), (uint32_t)(i / kStages) & 1u, p.status);
+        if (!__all_sync(0xffffffffu, ready)) break;
+        const int key0 = i * kBN;
+        const bool tail = key0 + kBN > len_k;   // tile holds slots past the sequence end
+        const uint32_t k_lo = smem_u32(ring) + s * kStageBytes;
+        const uint32_t v_lo = k_lo + 2 * kHalfBytes;
+        if (paged && tail) {
+            // Dead slots of the last page may hold anything; zero their V rows once per CTA
+            // before any warp multiplies by them.
+            const int dead0 = len_k - key0;
+            for (int idx = threadIdx.x; idx < (kBN - dead0) * 16; idx += kConsumerThreads) {
+                const int row = dead0 + (idx >> 4), pk = idx & 15;
+                const uint32_t a = swz128(v_lo + (pk >> 3) * kHalfBytes, row, pk & 7);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0u) : "memory");
+            }
+            fence_proxy_async_smem();
+            consumer_sync();
+        }
+        const bool skip = p.causal && !(paged && tail) && key0 > row_lo + 15 + off;
+        if (!skip) {
+            float sc[kBN / 8][4];
+#pragma unroll
+            for (int nt = 0; nt < kBN / 8; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < kHeadDim / 16; ++ks) {
+                const int pk = 2 * ks + (mi & 1);
+#pragma unroll
+                for (int np = 0; np < kBN / 16; ++np) {
+                    const int row = np * 16 + (mi >> 1) * 8 + r8;
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(swz128(k_lo + (pk >> 3) * kHalfBytes, row, pk & 7), b0, b1, b2, b3);
+                    mma16816<T>(sc[2 * np], qa[ks], b0, b1);
+                    mma16816<T>(sc[2 * np + 1], qa[ks], b2, b3);
+                }
+            }
+            const bool need_mask = tail || (p.causal && key0 + kBN - 1 > row_lo + off);
+            if (need_mask) {
+#pragma unroll
+                for (int nt = 0; nt < kBN / 8; ++nt)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int key = key0 + nt * 8 + 2 * t + (j & 1);
+                        if (key > (j < 2 ? lim0 : lim1)) sc[nt][j] = -INFINITY;
+                    }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < kBN / 8; ++nt) {
+                mx0 = fmaxf(mx0, fmaxf(sc[nt][0], sc[nt][1]));
+                mx1 = fmaxf(mx1, fmaxf(sc[nt][2], sc[nt][3]));
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0r, mx0 * c), mn1 = fmaxf(m1r, mx1 * c);
+            // A row that has seen no key yet keeps m = -inf; subtract 0 instead to stay finite.
+            const float sub0 = mn0 == -INFINITY ? 0.f : mn0, sub1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float corr0 = fast_exp2(m0r - sub0), corr1 = fast_exp2(m1r - sub1);
+            m0r = mn0; m1r = mn1;
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < kBN / 8; ++nt) {
+                sc[nt][0] = fast_exp2(fmaf(sc[nt][0], c, -sub0));
+                sc[nt][1] = fast_exp2(fmaf(sc[nt][1], c, -sub0));
+                sc[nt][2] = fast_exp2(fmaf(sc[nt][2], c, -sub1));
+                sc[nt][3] = fast_exp2(fmaf(sc[nt][3], c, -sub1));
+                ps0 += sc[nt][0] + sc[nt][1];
+                ps1 += sc[nt][2] + sc[nt][3];
+            }
+            l0 = fmaf(l0, corr0, ps0);
+            l1 = fmaf(l1, corr1, ps1);
+            if (__any_sync(0xffffffffu, corr0 != 1.f || corr1 != 1.f)) {
+#pragma unroll
+                for (int nt = 0; nt < kHeadDim / 8; ++nt) {
+                    o[nt][0] *= corr0; o[nt][1] *= corr0;
+                    o[nt][2] *= corr1; o[nt][3] *= corr1;
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < kBN / 16; ++kk) {
+                uint32_t pa[4];
+                pa[0] = pack2<T>(sc[2 * kk][0], sc[2 * kk][1]);
+                pa[1] = pack2<T>(sc[2 * kk][2], sc[2 * kk][3]);
+                pa[2] = pack2<T>(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+                pa[3] = pack2<T>(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+                const int row = kk * 16 + (mi & 1) * 8 + r8;
+#pragma unroll
+                for (int np = 0; np < kHeadDim / 16; ++np) {
+                    const int pk = 2 * np + (mi >> 1);
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4_trans(swz128(v_lo + (pk >> 3) * kHalfBytes, row, pk & 7), b0, b1, b2, b3);
+                    mma16816<T>(o[2 * np], pa, b0, b1);
+                    mma16816<T>(o[2 * np + 1], pa, b2, b3);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(empty_bar + s));
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    // Stage the warp's 16 x 128 block in its own (already consumed) slice of the Q buffer so
+    // that global stores are 16 bytes per lane and cover whole rows.
+    uint8_t* stage = q_smem + warp * (16 * 256);
+    consumer_sync();   // every warp has lifted its Q fragments out of the buffer
+#pragma unroll
+    for (int nt = 0; nt < kHeadDim / 8; ++nt) {
+        *reinterpret_cast<uint32_t*>(stage + g * 256 + ((nt ^ g) << 4) + t * 4) =
+            pack2<T>(o[nt][0] * inv0, o[nt][1] * inv0);
+        *reinterpret_cast<uint32_t*>(stage + (g + 8) * 256 + ((nt ^ g) << 4) + t * 4) =
+            pack2<T>(o[nt][2] * inv1, o[nt][3] * inv1);
+    }
+    __syncwarp();
+    T* ob = reinterpret_cast<T*>(p.out) + (int64_t)hq_idx * p.out_stride_h;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+        const int r = it * 2 + (lane >> 4), pk = lane & 15;
+        const int qrow = row_lo + r;
+        if (qrow < len_q) {
+            const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 256 + ((pk ^ (r & 7)) << 4));
+            *reinterpret_cast<uint4*>(ob + (int64_t)(q_begin + qrow) * p.out_stride_t + pk * 8) = v;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace b200mops
+
+using namespace b200mops;
+
+extern "C" int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* a, void* stream) {
+    if (!a) return B200MOPS_ERR_NULL_POINTER;
+    if (a->dtype != B200MOPS_BF16 && a->dtype != B200MOPS_F16) return B200MOPS_ERR_DTYPE;
+    if (a->batch < 0 || a->total_q < 0 || a->total_k < 0 || a->hq <= 0 || a->hkv <= 0 ||
+        a->max_seqlen_q < 0 || a->batch > 65535 || a->hq > 65535 || a->total_q > INT32_MAX ||
+        a->total_k > INT32_MAX)
+        return B200MOPS_ERR_SHAPE;
+    if (a->batch == 0 || a->total_q == 0 || a->max_seqlen_q == 0) return B200MOPS_OK;
+    if (a->head_dim != kHeadDim) return B200MOPS_ERR_HEAD_DIM;
+    if (a->hq % a->hkv != 0) return B200MOPS_ERR_GQA;
+    if (!a->q || !a->k || !a->v || !a->out || !a->cu_seqlens_q || !a->cu_seqlens_k)
+        return B200MOPS_ERR_NULL_POINTER;
+    if (!(a->softmax_scale > 0.f)) return B200MOPS_ERR_UNSUPPORTED;
+    const bool paged = a->block_table != nullptr;
+    if (paged) {
+        if (a->page <= 0 || a->num_blocks <= 0 || a->max_blocks_per_seq <= 0) return B200MOPS_ERR_SHAPE;
+        if (a->page % kBN != 0) return B200MOPS_ERR_PAGE_SIZE;
+        if (a->table_stride0 < a->max_blocks_per_seq) return B200MOPS_ERR_STRIDE;
+    }
+    if (a->q_stride_h < kHeadDim || a->k_stride_h < kHeadDim || a->v_stride_h < kHeadDim ||
+        a->out_stride_h < kHeadDim || a->q_stride_t <= 0 || a->k_stride_t <= 0 ||
+        a->v_stride_t <= 0 || a->out_stride_t <= 0)
+        return B200MOPS_ERR_STRIDE;
+    if (!aligned16(a->out) || (a->out_stride_t % 8) || (a->out_stride_h % 8))
+        return B200MOPS_ERR_ALIGNMENT;
+
+    CUtensorMap tm_q, tm_k, tm_v;
+    {
+        const uint64_t dims[4] = {(uint64_t)kHeadDim, (uint64_t)a->hq, (uint64_t)a->total_q, 1};
+        const uint64_t st[3] = {(uint64_t)a->q_stride_h * 2, (uint64_t)a->q_stride_t * 2,
+                                (uint64_t)a->q_stride_t * 2 * (uint64_t)a->total_q};
+        const uint32_t box[4] = {64, 1, (uint32_t)kBM, 1};
+        const int rc = encode_map_16bit(&tm_q, a->dtype, a->q, 4, dims, st, box);
+        if (rc != B200MOPS_OK) return rc;
+    }
+    {
+        const uint64_t rows = paged ? (uint64_t)a->page : (uint64_t)a->total_k;
+        const uint64_t blocks = paged ? (uint64_t)a->num_blocks : 1;
+        const uint64_t dims[4] = {(uint64_t)kHeadDim, (uint64_t)a->hkv, rows, blocks};
+        const uint32_t box[4] = {64, 1, (uint32_t)kBN, 1};
+        const uint64_t ks[3] = {(uint64_t)a->k_stride_h * 2, (uint64_t)a->k_stride_t * 2,
+                                paged ? (uint64_t)a->k_stride_block * 2
+                                      : (uint64_t)a->k_stride_t * 2 * rows};
+        const uint64_t vs[3] = {(uint64_t)a->v_stride_h * 2, (uint64_t)a->v_stride_t * 2,
+                                paged ? (uint64_t)a->v_stride_block * 2
+                                      : (uint64_t)a->v_stride_t * 2 * rows};
+        if (paged && (a->k_stride_block <= 0 || a->v_stride_block <= 0)) return B200MOPS_ERR_STRIDE;
+        if (rows == 0) return B200MOPS_ERR_SHAPE;
+        int rc = encode_map_16bit(&tm_k, a->dtype, a->k, 4, dims, ks, box);
+        if (rc != B200MOPS_OK) return rc;
+        rc = encode_map_16bit(&tm_v, a->dtype, a->v, 4, dims, vs, box);
+        if (rc != B200MOPS_OK) return rc;
+    }
+
+    PrefillParams p;
+    p.out = a->out; p.out_stride_t = a->out_stride_t; p.out_stride_h = a->out_stride_h;
+    p.cu_q = a->cu_seqlens_q; p.cu_k = a->cu_seqlens_k;
+    p.table = a->block_table; p.table_stride = a->table_stride0;
+    p.group = (int)(a->hq / a->hkv);
+    p.page = (int)a->page; p.num_blocks = (int)a->num_blocks;
+    p.causal = a->causal ? 1 : 0;
+    p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+    p.status = a->status_word;
+
+    const dim3 grid((unsigned)((a->max_seqlen_q + kBM - 1) / kBM), (unsigned)a->hq, (unsigned)a->batch);
+    cudaStream_t st = as_stream(stream);
+    if (a->dtype == B200MOPS_BF16) {
+        if (cudaFuncSetAttribute(varlen_prefill_kernel<__nv_bfloat16>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return B200MOPS_ERR_LAUNCH;
+        varlen_prefill_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, st>>>(tm_q, tm_k, tm_v, p);
+    } else {
+        if (cudaFuncSetAttribute(varlen_prefill_kernel<__half>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return B200MOPS_ERR_LAUNCH;
+        varlen_prefill_kernel<__half><<<grid, kThreads, kSmemBytes, st>>>(tm_q, tm_k, tm_v, p);
+    }
+    return launch_status();
+}

@@ -1,0 +1,367 @@
+"""Drop-in `mops` operator surface backed by the sm_100a C-ABI library.
+
+Exports the same eleven names, with the same positional order and keyword names, that the
+reference binds in mops/__init__.py:15-26 and that nanovllm/layers/* import at module load.
+There is no backend registry and no switch: every name is bound directly to a function that
+validates its tensors, allocates the outputs through torch (so calls stay CUDA-graph
+capturable) and launches one hand-written kernel on torch's current stream.  CPU tensors are
+rejected -- this backend has no CPU path.
+
+Use it either as `nano_vllm_ninetoothed_b200.mops` or, for unmodified callers that say
+`from mops import ...`, after `nano_vllm_ninetoothed_b200.install_as_mops()`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+
+import torch
+
+from .. import _cabi
+from .._cabi import PagedDecodeArgs, VarlenPrefillArgs, check, lib
+
+__all__ = [
+    "linear", "rms_forward", "add_rms_forward", "softmax", "siluAndMul", "sampler_forward",
+    "apply_rotary_emb", "embedding", "store_kvcache", "flash_attn_varlen_func",
+    "flash_attn_with_kvcache", "device_status", "reset_device_status",
+]
+
+_DTYPES = {torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16, torch.float32: _cabi.F32}
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def _dtype(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"b200 mops: unsupported dtype {t.dtype}") from None
+
+
+def _need_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("b200 mops: tensors must live on a CUDA device (no CPU path exists)")
+        if t.device != dev:
+            raise RuntimeError("b200 mops: all tensors of a call must be on the same device")
+    return dev
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _status_word(dev: torch.device) -> int:
+    """Device int32 that kernels OR diagnostic bits into (bad slot / id / page, wait timeout).
+
+    It is created on the first call for a device, so make that call before any graph capture.
+    """
+    w = _status_words.get(dev.index)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status_words[dev.index] = w
+    return w.data_ptr()
+
+
+def device_status(device=None) -> int:
+    """Read (and synchronise on) the diagnostic bits accumulated by kernels on `device`."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    w = _status_words.get(idx)
+    return 0 if w is None else int(w.item())
+
+
+def reset_device_status(device=None) -> None:
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    w = _status_words.get(idx)
+    if w is not None:
+        w.zero_()
+
+
+# --------------------------------------------------------------------------- library GEMM
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """`x @ weight.T (+ bias)` through cuBLAS, exactly as the reference's torch backend does
+    (mops/torch/ops.py:5-7); a plain library GEMM, not one of this package's kernels."""
+    _need_cuda(x, weight)
+    return torch.nn.functional.linear(x, weight, bias)
+
+
+# The reference's torch backend has no `softmax` either (mops/registry.py:36-39 returns None),
+# and nothing in nanovllm imports it.
+softmax = None
+
+
+# --------------------------------------------------------------------------- norms
+def _rows2(x: torch.Tensor):
+    """(tensor, rows0, rows1, stride0, stride1) with the last dim dense."""
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    if x.dim() == 1:
+        return x, 1, 1, 0, 0
+    if x.dim() == 2:
+        return x, x.shape[0], 1, x.stride(0), 0
+    if x.dim() == 3:
+        return x, x.shape[0], x.shape[1], x.stride(0), x.stride(1)
+    x = x.contiguous()
+    n = x.shape[-1]
+    return x, x.numel() // n, 1, n, 0
+
+
+def rms_forward(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMSNorm over the last dim (mops/torch/ops.py:9-16).  Accepts the strided
+    `[T, H, 128]` q/k views of the qkv activation; returns a fresh contiguous tensor."""
+    dev = _need_cuda(x, weight)
+    shape = x.shape
+    x, rows0, rows1, s0, s1 = _rows2(x)
+    n = shape[-1]
+    weight = weight if weight.dtype == x.dtype else weight.to(x.dtype)
+    out = torch.empty(shape, dtype=x.dtype, device=dev)
+    check("b200mops_rmsnorm", lib.b200mops_rmsnorm(
+        x.data_ptr(), rows0, rows1, s0, s1, weight.data_ptr(), float(eps), out.data_ptr(), n,
+        _dtype(x), _stream(dev)))
+    return out
+
+
+def add_rms_forward(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
+                    eps: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """Fused residual add + RMSNorm (mops/torch/ops.py:18-30): returns
+    `(normed, x + residual)`, both fresh tensors in the input dtype."""
+    dev = _need_cuda(x, residual, weight)
+    if x.shape != residual.shape or x.dtype != residual.dtype:
+        raise ValueError("add_rms_forward: x and residual must match in shape and dtype")
+    shape = x.shape
+    n = shape[-1]
+    x2 = x.reshape(-1, n)
+    r2 = residual.reshape(-1, n)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    if r2.stride(-1) != 1:
+        r2 = r2.contiguous()
+    weight = weight if weight.dtype == x.dtype else weight.to(x.dtype)
+    out = torch.empty(shape, dtype=x.dtype, device=dev)
+    res_out = torch.empty(shape, dtype=x.dtype, device=dev)
+    check("b200mops_add_rmsnorm", lib.b200mops_add_rmsnorm(
+        x2.data_ptr(), r2.data_ptr(), x2.shape[0], n, x2.stride(0), r2.stride(0),
+        weight.data_ptr(), float(eps), out.data_ptr(), res_out.data_ptr(), _dtype(x), _stream(dev)))
+    return out, res_out
+
+
+# --------------------------------------------------------------------------- elementwise
+def siluAndMul(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """`silu(x) * y` (mops/torch/ops.py:32-34); x and y are usually the two strided halves of
+    the gate_up activation (nanovllm/layers/activation.py:14-16)."""
+    dev = _need_cuda(x, y)
+    if x.shape != y.shape or x.dtype != y.dtype:
+        raise ValueError("siluAndMul: x and y must match in shape and dtype")
+    shape = x.shape
+    n = shape[-1]
+    if x.dim() != 2:
+        x, y = x.reshape(-1, n), y.reshape(-1, n)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    if y.stride(-1) != 1:
+        y = y.contiguous()
+    out = torch.empty(shape, dtype=x.dtype, device=dev)
+    check("b200mops_silu_mul", lib.b200mops_silu_mul(
+        x.data_ptr(), y.data_ptr(), x.shape[0], n, x.stride(0), y.stride(0), out.data_ptr(),
+        _dtype(x), _stream(dev)))
+    return out
+
+
+def apply_rotary_emb(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """NeoX half-split rotation (mops/torch/ops.py:45-54).  x is `[T, H, d]`; cos and sin are
+    fp32 `[T, 1, d/2]` (views of one cos|sin cache row per token); returns a new tensor."""
+    dev = _need_cuda(x, cos, sin)
+    if x.dim() != 3:
+        raise ValueError("apply_rotary_emb: x must be [tokens, heads, head_dim]")
+    tokens, heads, hd = x.shape
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    cos2 = cos.reshape(tokens, hd // 2) if cos.dim() != 2 else cos
+    sin2 = sin.reshape(tokens, hd // 2) if sin.dim() != 2 else sin
+    if cos2.dtype != torch.float32:
+        cos2, sin2 = cos2.float(), sin2.float()
+    if cos2.stride(-1) != 1 or sin2.stride(-1) != 1 or cos2.stride(0) != sin2.stride(0):
+        cos2, sin2 = cos2.contiguous(), sin2.contiguous()
+    out = torch.empty((tokens, heads, hd), dtype=x.dtype, device=dev)
+    check("b200mops_rope_neox", lib.b200mops_rope_neox(
+        x.data_ptr(), tokens, heads, hd, x.stride(0), x.stride(1), cos2.data_ptr(), sin2.data_ptr(),
+        cos2.stride(0), out.data_ptr(), _dtype(x), _stream(dev)))
+    return out
+
+
+def sampler_forward(logits: torch.Tensor, temperatures: torch.Tensor) -> torch.Tensor:
+    """Greedy token choice: argmax over `logits / T` per row, lowest index on ties -- the value
+    of `argmax(softmax(logits / T))` in mops/torch/ops.py:37-43.  Returns int64 `[rows]`."""
+    dev = _need_cuda(logits, temperatures)
+    if logits.dim() != 2:
+        raise ValueError("sampler_forward: logits must be [rows, vocab]")
+    rows, vocab = logits.shape
+    if logits.stride(-1) != 1:
+        logits = logits.contiguous()
+    temps = temperatures if temperatures.dtype == torch.float32 else temperatures.float()
+    temps = temps.contiguous()
+    out = torch.empty(rows, dtype=torch.int64, device=dev)
+    ws_bytes = lib.b200mops_sample_argmax_workspace_bytes(rows, vocab)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    check("b200mops_sample_argmax", lib.b200mops_sample_argmax(
+        logits.data_ptr(), rows, vocab, logits.stride(0), temps.data_ptr(), out.data_ptr(),
+        ws.data_ptr(), ws_bytes, _dtype(logits), _stream(dev)))
+    return out
+
+
+# --------------------------------------------------------------------------- indexed row movers
+def embedding(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """`weight[x]` row gather (mops/torch/ops.py:57-59); ids of any integer dtype and shape."""
+    dev = _need_cuda(x, weight)
+    if weight.dim() != 2:
+        raise ValueError("embedding: weight must be [vocab, hidden]")
+    ids = x if x.dtype == torch.int64 else x.long()
+    ids = ids.contiguous()
+    if weight.stride(1) != 1:
+        weight = weight.contiguous()
+    vocab, hidden = weight.shape
+    out = torch.empty((*x.shape, hidden), dtype=weight.dtype, device=dev)
+    check("b200mops_embedding", lib.b200mops_embedding(
+        ids.data_ptr(), ids.numel(), weight.data_ptr(), vocab, hidden, weight.stride(0),
+        out.data_ptr(), _dtype(weight), _status_word(dev), _stream(dev)))
+    return out
+
+
+def store_kvcache(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor,
+                  v_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """Scatter this step's K/V rows into the paged caches at `slot_mapping` (-1 = skip).
+    Same layout contract as the reference kernel asserts (mops/triton/attention.py:31-38)."""
+    dev = _need_cuda(key, value, k_cache, v_cache, slot_mapping)
+    n, heads, hd = key.shape
+    d = heads * hd
+    assert key.stride(-1) == 1 and value.stride(-1) == 1
+    assert key.stride(1) == hd and value.stride(1) == hd
+    assert k_cache.stride(1) == d and v_cache.stride(1) == d
+    assert k_cache.stride(0) == k_cache.shape[1] * d and v_cache.stride(0) == v_cache.shape[1] * d
+    assert slot_mapping.numel() == n
+    assert key.dtype == value.dtype == k_cache.dtype == v_cache.dtype
+    if slot_mapping.dtype != torch.int32:
+        slot_mapping = slot_mapping.to(torch.int32)
+    slot_mapping = slot_mapping.contiguous()
+    check("b200mops_store_kvcache", lib.b200mops_store_kvcache(
+        key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0),
+        k_cache.data_ptr(), v_cache.data_ptr(), d, slot_mapping.data_ptr(), n, d,
+        k_cache.shape[0] * k_cache.shape[1], _dtype(key), _status_word(dev), _stream(dev)))
+
+
+# --------------------------------------------------------------------------- attention
+def _i32(t: torch.Tensor) -> torch.Tensor:
+    return (t if t.dtype == torch.int32 else t.to(torch.int32)).contiguous()
+
+
+def flash_attn_with_kvcache(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                            cache_seqlens: torch.Tensor | None = None,
+                            block_table: torch.Tensor | None = None,
+                            softmax_scale: float | None = None, causal: bool = False,
+                            chunk_tokens: int = 0, **_ignored) -> torch.Tensor:
+    """Paged decode attention, one query token per sequence (mops/torch/ops.py:74-76, semantics
+    at :78-125; called from nanovllm/layers/attention.py:40-42).
+
+    q `[B, 1, Hq, 128]`; caches `[num_blocks, page, Hkv, 128]`; `cache_seqlens` int32 `[B]`
+    counts the token being decoded; `block_table` int32 `[B, max_blocks]`, padded with -1.
+    With a single query token `causal` changes nothing.  Returns `[B, 1, Hq, 128]`.
+    """
+    if cache_seqlens is None or block_table is None:
+        raise ValueError("flash_attn_with_kvcache: cache_seqlens and block_table are required")
+    dev = _need_cuda(q, k_cache, v_cache, cache_seqlens, block_table)
+    if q.dim() != 4 or q.shape[1] != 1:
+        raise ValueError("flash_attn_with_kvcache: q must be [batch, 1, heads, head_dim]")
+    if k_cache.shape != v_cache.shape or k_cache.dim() != 4:
+        raise ValueError("flash_attn_with_kvcache: caches must be [blocks, page, kv_heads, head_dim]")
+    if not (q.dtype == k_cache.dtype == v_cache.dtype):
+        raise TypeError("flash_attn_with_kvcache: q and the caches must share a dtype")
+    batch, _, hq, hd = q.shape
+    nb, page, hkv, _ = k_cache.shape
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    assert k_cache.stride(-1) == 1 and v_cache.stride(-1) == 1
+    lens = _i32(cache_seqlens)
+    table = _i32(block_table)
+    max_blocks = table.shape[1]
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(hd)
+    out = torch.empty_like(q)
+    if batch == 0 or max_blocks == 0:
+        return out.zero_()
+    ws_bytes = lib.b200mops_paged_decode_workspace_bytes(batch, hq, hkv, hd, page, max_blocks,
+                                                         chunk_tokens)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+    args = PagedDecodeArgs(
+        q=q.data_ptr(), q_stride_b=q.stride(0), q_stride_h=q.stride(2),
+        out=out.data_ptr(), out_stride_b=out.stride(0), out_stride_h=out.stride(2),
+        k_cache=k_cache.data_ptr(), k_stride_block=k_cache.stride(0),
+        k_stride_token=k_cache.stride(1), k_stride_head=k_cache.stride(2),
+        v_cache=v_cache.data_ptr(), v_stride_block=v_cache.stride(0),
+        v_stride_token=v_cache.stride(1), v_stride_head=v_cache.stride(2),
+        cache_seqlens=lens.data_ptr(), block_table=table.data_ptr(), table_stride0=table.stride(0),
+        batch=batch, hq=hq, hkv=hkv, head_dim=hd, page=page, num_blocks=nb,
+        max_blocks_per_seq=max_blocks, softmax_scale=scale, chunk_tokens=chunk_tokens,
+        workspace=ws.data_ptr() if ws is not None else None, workspace_bytes=ws_bytes,
+        status_word=_status_word(dev), dtype=_dtype(q))
+    check("b200mops_paged_decode", lib.b200mops_paged_decode(C.byref(args), _stream(dev)))
+    return out
+
+
+def flash_attn_varlen_func(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                           cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor,
+                           max_seqlen_q: int, max_seqlen_k: int | None = None,
+                           dropout_p: float = 0.0, softmax_scale: float | None = None,
+                           causal: bool = False, block_table: torch.Tensor | None = None,
+                           **_ignored) -> torch.Tensor:
+    """Variable-length (packed) attention, causal mask aligned bottom-right
+    (mops/torch/ops.py:70-72; called from nanovllm/layers/attention.py:31-37).
+
+    q `[total_q, Hq, 128]`; k, v `[total_k, Hkv, 128]` (v may be a strided view), or -- with
+    `block_table` -- the paged caches `[num_blocks, page, Hkv, 128]` for prefix-cache prefill.
+    `max_seqlen_k` is accepted and not needed.  Returns `[total_q, Hq, 128]`.
+    """
+    if dropout_p != 0.0:
+        raise NotImplementedError("flash_attn_varlen_func: dropout is not supported")
+    dev = _need_cuda(q, k, v, cu_seqlens_q, cu_seqlens_k)
+    if q.dim() != 3:
+        raise ValueError("flash_attn_varlen_func: q must be [total_q, heads, head_dim]")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("flash_attn_varlen_func: q, k and v must share a dtype")
+    total_q, hq, hd = q.shape
+    cu_q, cu_k = _i32(cu_seqlens_q), _i32(cu_seqlens_k)
+    batch = cu_q.numel() - 1
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(hd)
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    if k.stride(-1) != 1:
+        k = k.contiguous()
+    if v.stride(-1) != 1:
+        v = v.contiguous()
+    out = torch.empty((total_q, hq, hd), dtype=q.dtype, device=dev)
+    args = VarlenPrefillArgs(
+        q=q.data_ptr(), q_stride_t=q.stride(0), q_stride_h=q.stride(1),
+        out=out.data_ptr(), out_stride_t=out.stride(0), out_stride_h=out.stride(1),
+        cu_seqlens_q=cu_q.data_ptr(), cu_seqlens_k=cu_k.data_ptr(),
+        batch=batch, total_q=total_q, max_seqlen_q=int(max_seqlen_q),
+        max_seqlen_k=int(max_seqlen_k or 0), hq=hq, head_dim=hd,
+        softmax_scale=scale, causal=1 if causal else 0,
+        status_word=_status_word(dev), dtype=_dtype(q))
+    if block_table is None:
+        if k.dim() != 3 or v.shape != k.shape:
+            raise ValueError("flash_attn_varlen_func: k and v must be [total_k, kv_heads, head_dim]")
+        args.k, args.k_stride_t, args.k_stride_h = k.data_ptr(), k.stride(0), k.stride(1)
+        args.v, args.v_stride_t, args.v_stride_h = v.data_ptr(), v.stride(0), v.stride(1)
+        args.total_k, args.hkv = k.shape[0], k.shape[1]
+    else:
+        if k.dim() != 4 or v.shape != k.shape:
+            raise ValueError("flash_attn_varlen_func: paged k and v must be [blocks, page, kv_heads, head_dim]")
+        table = _i32(block_table)
+        args.k, args.k_stride_block, args.k_stride_t, args.k_stride_h = (
+            k.data_ptr(), k.stride(0), k.stride(1), k.stride(2))
+        args.v, args.v_stride_block, args.v_stride_t, args.v_stride_h = (
+            v.data_ptr(), v.stride(0), v.stride(1), v.stride(2))
+        args.block_table, args.table_stride0 = table.data_ptr(), table.stride(0)
+        args.num_blocks, args.page, args.hkv = k.shape[0], k.shape[1], k.shape[2]
+        args.max_blocks_per_seq = table.shape[1]
+        args.total_k = k.shape[0] * k.shape[1]
+    check("b200mops_varlen_prefill", lib.b200mops_varlen_prefill(C.byref(args), _stream(dev)))
+    return out

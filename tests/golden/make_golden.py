@@ -1,0 +1,107 @@
+"""Generate `tests/golden/torch_backend.pt` from the UNMODIFIED reference torch backend.
+
+Run in a container that has the reference tree (default `/root/reference`, or pass its path):
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+The reference's `mops/__init__.py` imports all three backends unconditionally, and two of
+them need packages that are not installed (`icecream`, `ninetoothed`).  Stub modules are put
+into `sys.modules` for those two names only, `BACKEND=torch` is selected, and then the seven
+operators that the torch backend implements in plain torch (mops/torch/ops.py:5-59) are run
+on seeded CPU inputs.  Inputs are regenerated from their seeds by `golden_inputs()` at test
+time; the file stores the outputs plus a checksum of every input, so that a torch version
+with a different random stream is detected instead of producing false mismatches.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import sys
+import types
+from pathlib import Path
+from unittest import mock
+
+import torch
+
+HERE = Path(__file__).resolve().parent
+OUT = HERE / "torch_backend.pt"
+
+
+def tensor_digest(t: torch.Tensor) -> str:
+    raw = t.detach().contiguous().view(torch.uint8).numpy().tobytes()
+    return hashlib.sha256(raw).hexdigest()[:16]
+
+
+def golden_inputs() -> dict[str, dict]:
+    """Seeded inputs per case.  Pure function of torch's CPU random stream."""
+    cases: dict[str, dict] = {}
+    for dt_name, dt in (("bf16", torch.bfloat16), ("f32", torch.float32), ("f16", torch.float16)):
+        g = torch.Generator().manual_seed(1234)
+        x = torch.randn(11, 1024, generator=g).to(dt)
+        r = torch.randn(11, 1024, generator=g).to(dt)
+        w = (1.0 + 0.02 * torch.randn(1024, generator=g)).to(dt)
+        cases[f"add_rms_forward/{dt_name}"] = dict(x=x, residual=r, weight=w, eps=1e-6)
+        cases[f"rms_forward/{dt_name}"] = dict(x=x.clone(), weight=w, eps=1e-6)
+        # q/k-norm: strided [T, H, 128] view of a fused qkv activation
+        qkv = torch.randn(19, (4 + 2 * 2) * 128, generator=g).to(dt)
+        w128 = (1.0 + 0.02 * torch.randn(128, generator=g)).to(dt)
+        cases[f"rms_forward_qnorm/{dt_name}"] = dict(x=qkv[:, : 4 * 128].view(19, 4, 128), weight=w128,
+                                                     eps=1e-6)
+        gate_up = torch.randn(5, 2 * 3072, generator=g).to(dt)
+        a, b = gate_up.chunk(2, -1)
+        cases[f"siluAndMul/{dt_name}"] = dict(x=a, y=b)
+        xr = torch.randn(13, 6, 128, generator=g).to(dt)
+        pos = torch.randint(0, 4096, (13,), generator=g)
+        inv_freq = 1.0 / (1000000.0 ** (torch.arange(0, 128, 2, dtype=torch.float) / 128))
+        freqs = torch.einsum("i,j->ij", torch.arange(4096, dtype=torch.float), inv_freq)
+        cache = torch.cat((freqs.cos(), freqs.sin()), dim=-1).unsqueeze(1)
+        cos, sin = cache[pos].chunk(2, dim=-1)
+        cases[f"apply_rotary_emb/{dt_name}"] = dict(x=xr, cos=cos, sin=sin)
+        table = (0.02 * torch.randn(5000, 256, generator=g)).to(dt)
+        ids = torch.randint(0, 5000, (77,), generator=g)
+        ids[0], ids[1] = 0, 4999
+        cases[f"embedding/{dt_name}"] = dict(x=ids, weight=table)
+        logits = torch.randn(9, 15193, generator=g).to(dt)
+        logits[3, 100] = logits[3].max()        # force an exact tie: first index must win
+        logits[3, 9000] = logits[3, 100]
+        temps = torch.rand(9, generator=g) + 0.3
+        cases[f"sampler_forward/{dt_name}"] = dict(logits=logits, temperatures=temps)
+    return cases
+
+
+def call_case(ops, name: str, kw: dict):
+    op = name.split("/")[0]
+    fn = {"rms_forward_qnorm": "rms_forward"}.get(op, op)
+    # The reference mutates fp32 inputs in place in two ops; give it private copies.
+    kw = {k: (v.clone() if isinstance(v, torch.Tensor) and v.is_contiguous() else v) for k, v in kw.items()}
+    return getattr(ops, fn)(**kw)
+
+
+def load_reference_torch_backend(ref_root: str):
+    os.environ["BACKEND"] = "torch"
+    sys.path.insert(0, ref_root)
+    sys.modules.setdefault("icecream", types.SimpleNamespace(ic=lambda *a, **k: None))
+    nt = mock.MagicMock()
+    for name in ("ninetoothed", "ninetoothed.language"):
+        sys.modules.setdefault(name, nt)
+    import mops  # noqa: F401  (the reference package)
+    import mops.torch.ops as ref_ops
+    assert Path(ref_ops.__file__).resolve().is_relative_to(Path(ref_root).resolve())
+    return ref_ops
+
+
+def main() -> None:
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_ops = load_reference_torch_backend(ref_root)
+    record = {"torch_version": str(torch.__version__), "outputs": {}, "input_digests": {}}
+    for name, kw in golden_inputs().items():
+        record["input_digests"][name] = {k: tensor_digest(v) for k, v in kw.items()
+                                         if isinstance(v, torch.Tensor)}
+        out = call_case(ref_ops, name, kw)
+        record["outputs"][name] = [o.clone() for o in (out if isinstance(out, tuple) else (out,))]
+    torch.save(record, OUT)
+    print(f"wrote {OUT} ({OUT.stat().st_size / 1024:.0f} KiB, {len(record['outputs'])} cases)")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,112 @@
+"""The C-ABI shared library on a machine without a GPU: it builds, loads, exports every symbol
+the header declares, and rejects bad arguments before touching CUDA."""
+from __future__ import annotations
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = ROOT / "include" / "b200mops.h"
+
+
+def _declared_functions() -> set[str]:
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return set(re.findall(r"\b(b200mops_[a-z0-9_]+)\s*\(", text))
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    lib = C.CDLL(str(built_library))
+    declared = _declared_functions()
+    assert declared, "no declarations parsed from the header"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in b200mops.h but not exported"
+
+
+def test_python_binding_lists_the_same_symbols(built_library):
+    from nano_vllm_ninetoothed_b200 import _cabi
+    assert set(_cabi.EXPORTED_SYMBOLS) == _declared_functions()
+    assert set(_cabi._SIGNATURES) == set(_cabi.EXPORTED_SYMBOLS)
+
+
+def test_struct_mirrors_match_header_field_order(built_library):
+    from nano_vllm_ninetoothed_b200 import _cabi
+    text = HEADER.read_text()
+    for struct, cls in (("b200mops_paged_decode_args", _cabi.PagedDecodeArgs),
+                        ("b200mops_varlen_prefill_args", _cabi.VarlenPrefillArgs)):
+        body = re.search(r"typedef struct " + struct + r" \{(.*?)\} " + struct, text, flags=re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        names = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            parts = decl.replace("*", " ").split(",")
+            names.append(parts[0].split()[-1])
+            names.extend(p.strip() for p in parts[1:])
+        assert names == [f[0] for f in cls._fields_], struct
+
+
+def test_abi_version_and_strerror(built_library):
+    from nano_vllm_ninetoothed_b200 import _cabi
+    assert _cabi.lib.b200mops_abi_version() == 1
+    assert _cabi.strerror(0) == "ok"
+    texts = {_cabi.strerror(i) for i in range(1, 15)}
+    assert len(texts) == 14 and "unknown b200mops status" not in texts
+    assert _cabi.strerror(999) == "unknown b200mops status"
+
+
+def test_argument_errors_are_reported_before_any_launch(built_library):
+    """None of these reach a CUDA call, so they run without a GPU."""
+    from nano_vllm_ninetoothed_b200 import _cabi
+    lib = _cabi.lib
+    # unknown dtype
+    assert lib.b200mops_store_kvcache(1, 1, 8, 8, 1, 1, 8, 1, 4, 8, 16, 99, None, None) == 2
+    # NULL pointers
+    assert lib.b200mops_store_kvcache(None, None, 8, 8, None, None, 8, None, 4, 8, 16, 0, None, None) == 1
+    # negative size
+    assert lib.b200mops_embedding(None, -1, None, 10, 8, 8, None, 0, None, None) == 3
+    # weight row stride shorter than the row
+    assert lib.b200mops_embedding(16, 4, 16, 10, 8, 4, 16, 0, None, None) == 4
+    # empty work is a successful no-op
+    assert lib.b200mops_embedding(None, 0, None, 10, 8, 8, None, 0, None, None) == 0
+    assert lib.b200mops_rmsnorm(None, 0, 1, 0, 0, None, 1e-6, None, 128, 0, None) == 0
+    a = _cabi.PagedDecodeArgs(batch=2, hq=4, hkv=2, head_dim=64, page=256, num_blocks=4,
+                              max_blocks_per_seq=2, dtype=0)
+    assert lib.b200mops_paged_decode(C.byref(a), None) == 6       # head_dim
+    a.head_dim, a.hq = 128, 5
+    assert lib.b200mops_paged_decode(C.byref(a), None) == 8       # hq % hkv
+    a.hq, a.page = 4, 100
+    assert lib.b200mops_paged_decode(C.byref(a), None) == 7       # page size
+    a.page, a.dtype = 256, 2
+    assert lib.b200mops_paged_decode(C.byref(a), None) == 2       # fp32 attention
+    a.dtype = 0
+    assert lib.b200mops_paged_decode(C.byref(a), None) == 1       # NULL tensors
+    p = _cabi.VarlenPrefillArgs(batch=1, total_q=8, total_k=8, max_seqlen_q=8, hq=4, hkv=2,
+                                head_dim=96, dtype=0)
+    assert lib.b200mops_varlen_prefill(C.byref(p), None) == 6
+    with pytest.raises(_cabi.B200MopsError) as e:
+        _cabi.check("b200mops_paged_decode", 7)
+    assert e.value.status == 7 and "page" in str(e.value)
+
+
+def test_decode_chunking_helpers(built_library):
+    from nano_vllm_ninetoothed_b200 import _cabi
+    lib = _cabi.lib
+    # large batch, long tables -> capped chunk, several splits, workspace for the partials
+    chunk = lib.b200mops_paged_decode_auto_chunk(256, 8, 256, 32)
+    assert chunk % 64 == 0 and 128 <= chunk <= 1024
+    nsplit = -(-32 * 256 // chunk)
+    assert lib.b200mops_paged_decode_workspace_bytes(256, 32, 8, 128, 256, 32, 0) == \
+        256 * 32 * nsplit * 130 * 4
+    # one short page per sequence -> a single split needs no workspace
+    assert lib.b200mops_paged_decode_auto_chunk(512, 8, 256, 1) == 256
+    assert lib.b200mops_paged_decode_workspace_bytes(512, 16, 8, 128, 256, 1, 0) == 0
+    # explicit chunk is rounded up to whole 64-token tiles
+    assert lib.b200mops_paged_decode_workspace_bytes(2, 4, 2, 128, 256, 4, 100) == \
+        2 * 4 * 8 * 130 * 4
+    # argmax scratch: 8 bytes per (row, split)
+    assert lib.b200mops_sample_argmax_workspace_bytes(8, 151936) % 8 == 0
+    assert lib.b200mops_sample_argmax_workspace_bytes(0, 151936) == 0

@@ -1,0 +1,261 @@
+"""GPU parity of paged decode and varlen prefill attention against the CPU oracle, through the
+C ABI.  Tolerance: 2e-2 absolute / 1e-2 relative on 16-bit outputs."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from nano_vllm_ninetoothed_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL = dict(atol=2e-2, rtol=1e-2)
+
+
+def close(got, want):
+    assert torch.isfinite(got).all(), "non-finite values in the kernel output"
+    torch.testing.assert_close(got.float().cpu(), want.float(), **TOL)
+
+
+def run_decode(mops, oracle, case, **kw):
+    d = case.to(DEV)
+    got = mops.flash_attn_with_kvcache(d.q, d.k_cache, d.v_cache, cache_seqlens=d.cache_seqlens,
+                                       block_table=d.block_table, softmax_scale=d.softmax_scale,
+                                       causal=True, **kw)
+    assert got.shape == case.q.shape and got.dtype == case.q.dtype
+    # the oracle must never look at dead slots either: give it a NaN-free copy check via lens
+    want = oracle.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                          cache_seqlens=case.cache_seqlens,
+                                          block_table=case.block_table.clamp(min=0),
+                                          softmax_scale=case.softmax_scale, causal=True)
+    close(got, want)
+    return got
+
+
+# ------------------------------------------------------------------ paged decode
+def test_decode_config1(mops, oracle):
+    """8 sequences, context in [128, 1024], 16 q / 8 kv heads, page 256, 64 physical blocks."""
+    case = W.make_decode_case(seed=0, batch=8, len_lo=128, len_hi=1024, hq=16, hkv=8, num_blocks=64)
+    run_decode(mops, oracle, case)
+    assert mops.device_status() == 0
+
+
+@pytest.mark.parametrize("chunk", [0, 64, 128, 192, 256, 512, 4096])
+def test_decode_page_boundaries_every_chunking(mops, oracle, chunk):
+    lens = [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 255, 256, 257, 511, 512, 513, 1000, 1024]
+    case = W.make_decode_case(seed=1, lens=lens, hq=8, hkv=2, poison=True)
+    run_decode(mops, oracle, case, chunk_tokens=chunk)
+
+
+@pytest.mark.parametrize("hq,hkv", [(1, 1), (2, 1), (4, 1), (8, 1), (16, 1), (8, 2), (16, 4),
+                                    (32, 8), (24, 8), (16, 8), (8, 8)])
+def test_decode_head_groupings(mops, oracle, hq, hkv):
+    """G = hq/hkv from 1 to 16 and the per-rank KV-head counts tensor parallelism produces."""
+    case = W.make_decode_case(seed=2, batch=5, len_lo=1, len_hi=700, hq=hq, hkv=hkv, poison=True)
+    run_decode(mops, oracle, case)
+
+
+def test_decode_zero_length_rows_and_stale_table_columns(mops, oracle):
+    """Graph-replay padding: context_lens 0 -> zero output rows; table columns past the live
+    pages hold stale or -1 ids and must never be dereferenced."""
+    case = W.make_decode_case(seed=3, lens=[300, 0, 40, 0, 700], hq=8, hkv=4, poison=True)
+    tbl = case.block_table.clone()
+    lens = case.cache_seqlens.tolist()
+    for b, n in enumerate(lens):
+        used = (n + 255) // 256
+        tbl[b, used:] = torch.tensor([-1, 10**6, -5][b % 3], dtype=torch.int32)
+    case.block_table = tbl
+    for chunk in (0, 128, 1024):
+        got = run_decode(mops, oracle, case, chunk_tokens=chunk)
+        assert not got[1].any() and not got[3].any()
+    assert mops.device_status() == 0      # dead columns were never read
+
+
+@pytest.mark.parametrize("page", [64, 128, 512])
+def test_decode_other_page_sizes(mops, oracle, page):
+    case = W.make_decode_case(seed=4, batch=6, len_lo=1, len_hi=900, hq=8, hkv=2, page=page,
+                              poison=True)
+    run_decode(mops, oracle, case)
+    run_decode(mops, oracle, case, chunk_tokens=64)
+
+
+def test_decode_fp16(mops, oracle):
+    case = W.make_decode_case(seed=5, batch=4, len_lo=1, len_hi=600, hq=8, hkv=2,
+                              dtype=torch.float16, poison=True)
+    run_decode(mops, oracle, case)
+
+
+def test_decode_layer_views_of_one_kv_allocation(mops, oracle):
+    """Caches handed over as [layer] views of a [2, L, NB, P, H, d] tensor."""
+    case = W.make_decode_case(seed=6, batch=4, len_lo=100, len_hi=600, hq=4, hkv=2)
+    pool = torch.zeros(2, 3, *case.k_cache.shape, dtype=torch.bfloat16, device=DEV)
+    pool[0, 1], pool[1, 1] = case.k_cache.to(DEV), case.v_cache.to(DEV)
+    got = mops.flash_attn_with_kvcache(case.q.to(DEV), pool[0, 1], pool[1, 1],
+                                       cache_seqlens=case.cache_seqlens.to(DEV),
+                                       block_table=case.block_table.to(DEV),
+                                       softmax_scale=case.softmax_scale, causal=True)
+    want = oracle.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                          cache_seqlens=case.cache_seqlens,
+                                          block_table=case.block_table,
+                                          softmax_scale=case.softmax_scale)
+    close(got, want)
+
+
+def test_decode_out_of_range_page_is_flagged_not_fatal(mops):
+    case = W.make_decode_case(seed=7, lens=[300], hq=4, hkv=2).to(DEV)
+    case.block_table[0, 1] = 10**6
+    out = mops.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                       cache_seqlens=case.cache_seqlens,
+                                       block_table=case.block_table,
+                                       softmax_scale=case.softmax_scale)
+    torch.cuda.synchronize()
+    assert mops.device_status() & 0x4
+    mops.reset_device_status()
+    assert torch.isfinite(out).all()
+
+
+def test_decode_constant_value_rows_full_size_property(mops):
+    """Size-independent property at the large-batch shape (256 sequences, context up to 8192,
+    32 q / 8 kv heads): if every V row of a KV head equals one vector, softmax weights summing
+    to one must return exactly that vector whatever the lengths and pages."""
+    lens = W.config_lens("decode_8b")
+    case = W.make_decode_case(seed=0, lens=lens, hq=32, hkv=8, device=DEV, cache_on_device=True)
+    g = torch.Generator(device=DEV).manual_seed(1)
+    const = torch.randn(8, 128, generator=g, device=DEV).bfloat16()
+    case.v_cache[:] = const
+    out = mops.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                       cache_seqlens=case.cache_seqlens,
+                                       block_table=case.block_table,
+                                       softmax_scale=case.softmax_scale, causal=True)
+    want = const.repeat_interleave(4, dim=0).expand(256, 32, 128)
+    torch.testing.assert_close(out[:, 0].float(), want.float(), atol=8e-3, rtol=8e-3)
+    assert mops.device_status() == 0
+
+
+def test_decode_full_size_sample_against_oracle(mops, oracle):
+    """Large-batch shape on the device; 12 sequences (shortest, longest, and a spread) are
+    pulled back and checked against the CPU oracle."""
+    lens = W.config_lens("decode_8b")
+    case = W.make_decode_case(seed=0, lens=lens, hq=32, hkv=8, device=DEV, cache_on_device=True)
+    out = mops.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                       cache_seqlens=case.cache_seqlens,
+                                       block_table=case.block_table,
+                                       softmax_scale=case.softmax_scale, causal=True)
+    order = sorted(range(len(lens)), key=lambda i: lens[i])
+    picks = sorted(set(order[:2] + order[-2:] + order[:: len(order) // 8]))
+    for b in picks:
+        nblk = (lens[b] + 255) // 256
+        ids = case.block_table[b, :nblk].long()
+        kc, vc = case.k_cache[ids].cpu(), case.v_cache[ids].cpu()
+        want = oracle.flash_attn_with_kvcache(
+            case.q[b:b + 1].cpu(), kc, vc, cache_seqlens=torch.tensor([lens[b]], dtype=torch.int32),
+            block_table=torch.arange(nblk, dtype=torch.int32).view(1, -1),
+            softmax_scale=case.softmax_scale)
+        close(out[b:b + 1], want)
+
+
+# ------------------------------------------------------------------ varlen prefill
+def run_prefill(mops, oracle, case, causal=True):
+    d = case if case.q.is_cuda else case.to(DEV)
+    got = mops.flash_attn_varlen_func(d.q, d.k, d.v, max_seqlen_q=d.max_seqlen,
+                                      cu_seqlens_q=d.cu_seqlens, max_seqlen_k=d.max_seqlen,
+                                      cu_seqlens_k=d.cu_seqlens, softmax_scale=d.softmax_scale,
+                                      causal=causal, block_table=None)
+    c = case if not case.q.is_cuda else case.to("cpu")
+    want = oracle.flash_attn_varlen_func(c.q, c.k, c.v, c.cu_seqlens, c.cu_seqlens, c.max_seqlen,
+                                         c.max_seqlen, softmax_scale=c.softmax_scale, causal=causal)
+    assert got.shape == case.q.shape and got.is_contiguous()
+    close(got, want)
+    return got
+
+
+def test_prefill_config2(mops, oracle):
+    """8 sequences in [64, 2048], 16 q / 8 kv heads; v is a strided slice of the qkv buffer."""
+    run_prefill(mops, oracle, W.make_prefill_case(seed=0, strided_v=True))
+    assert mops.device_status() == 0
+
+
+def test_prefill_tile_boundaries_and_single_tokens(mops, oracle):
+    lens = [1, 1, 2, 63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257, 300, 1, 513]
+    run_prefill(mops, oracle, W.make_prefill_case(seed=1, lens=lens, hq=4, hkv=2))
+
+
+@pytest.mark.parametrize("hq,hkv", [(1, 1), (4, 1), (4, 4), (8, 2), (6, 2)])
+def test_prefill_head_groupings(mops, oracle, hq, hkv):
+    run_prefill(mops, oracle, W.make_prefill_case(seed=2, batch=4, len_lo=1, len_hi=400, hq=hq,
+                                                  hkv=hkv, strided_v=True))
+
+
+def test_prefill_non_causal_and_fp16(mops, oracle):
+    run_prefill(mops, oracle, W.make_prefill_case(seed=3, lens=[50, 200, 129], hq=4, hkv=2), causal=False)
+    run_prefill(mops, oracle, W.make_prefill_case(seed=3, lens=[50, 200, 129], hq=4, hkv=2,
+                                                  dtype=torch.float16))
+
+
+def test_prefill_with_block_table_prefix_cache(mops, oracle):
+    """Prefix-cache prefill: new tokens attend to paged K/V that also hold a cached prefix;
+    causal mask aligned bottom-right; dead slots of the last page are NaN."""
+    g = torch.Generator().manual_seed(9)
+    total_lens = [700, 256, 300, 1025]
+    new_lens = [188, 256, 44, 1]
+    dec = W.make_decode_case(seed=9, lens=total_lens, hq=8, hkv=2, poison=True)
+    cu_q = torch.tensor([0] + list(torch.tensor(new_lens).cumsum(0)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(torch.tensor(total_lens).cumsum(0)), dtype=torch.int32)
+    q = torch.randn(sum(new_lens), 8, 128, generator=g).bfloat16()
+    want = oracle.flash_attn_varlen_func(q, dec.k_cache, dec.v_cache, cu_q, cu_k, max(new_lens),
+                                         max(total_lens), softmax_scale=dec.softmax_scale,
+                                         causal=True, block_table=dec.block_table.clamp(min=0))
+    d = dec.to(DEV)
+    got = mops.flash_attn_varlen_func(q.to(DEV), d.k_cache, d.v_cache, max_seqlen_q=max(new_lens),
+                                      cu_seqlens_q=cu_q.to(DEV), max_seqlen_k=max(total_lens),
+                                      cu_seqlens_k=cu_k.to(DEV), softmax_scale=dec.softmax_scale,
+                                      causal=True, block_table=d.block_table)
+    close(got, want)
+    assert mops.device_status() == 0
+
+
+def test_prefill_last_row_equals_decode_full_size(mops):
+    """Cross-kernel property at the Qwen3-8B prefill shape (16 sequences in [256, 4096], 32 q /
+    8 kv heads): the last causal row of each sequence is a decode step over the same keys."""
+    lens = W.config_lens("prefill_8b")
+    p = W.make_prefill_case(seed=0, lens=lens, hq=32, hkv=8, device=DEV)
+    out = mops.flash_attn_varlen_func(p.q, p.k, p.v, max_seqlen_q=p.max_seqlen,
+                                      cu_seqlens_q=p.cu_seqlens, max_seqlen_k=p.max_seqlen,
+                                      cu_seqlens_k=p.cu_seqlens, softmax_scale=p.softmax_scale,
+                                      causal=True)
+    nblk = [(n + 255) // 256 for n in lens]
+    kc = torch.zeros(sum(nblk), 256, 8, 128, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    table = torch.full((len(lens), max(nblk)), -1, dtype=torch.int32)
+    cur, last_rows = 0, []
+    for b, n in enumerate(lens):
+        s = int(p.cu_seqlens[b])
+        kc[cur:cur + nblk[b]].view(-1, 8, 128)[:n] = p.k[s:s + n]
+        vc[cur:cur + nblk[b]].view(-1, 8, 128)[:n] = p.v[s:s + n]
+        table[b, :nblk[b]] = torch.arange(cur, cur + nblk[b], dtype=torch.int32)
+        cur += nblk[b]
+        last_rows.append(s + n - 1)
+    dec = mops.flash_attn_with_kvcache(p.q[last_rows].unsqueeze(1), kc, vc,
+                                       cache_seqlens=torch.tensor(lens, dtype=torch.int32, device=DEV),
+                                       block_table=table.to(DEV), softmax_scale=p.softmax_scale,
+                                       causal=True)
+    torch.testing.assert_close(dec[:, 0].float(), out[last_rows].float(), **TOL)
+
+
+def test_prefill_full_size_heads_sample_against_oracle(mops, oracle):
+    """Qwen3-8B prefill shape on the device; q heads {0, 13, 31} (KV heads 0, 3, 7) of every
+    sequence are checked against the CPU oracle."""
+    lens = W.config_lens("prefill_8b")
+    p = W.make_prefill_case(seed=0, lens=lens, hq=32, hkv=8, device=DEV)
+    out = mops.flash_attn_varlen_func(p.q, p.k, p.v, max_seqlen_q=p.max_seqlen,
+                                      cu_seqlens_q=p.cu_seqlens, max_seqlen_k=p.max_seqlen,
+                                      cu_seqlens_k=p.cu_seqlens, softmax_scale=p.softmax_scale,
+                                      causal=True)
+    cu = p.cu_seqlens.cpu()
+    for hq_i in (0, 13, 31):
+        hk = hq_i // 4
+        want = oracle.flash_attn_varlen_func(p.q[:, hq_i:hq_i + 1].cpu(), p.k[:, hk:hk + 1].cpu(),
+                                             p.v[:, hk:hk + 1].cpu(), cu, cu, p.max_seqlen,
+                                             p.max_seqlen, softmax_scale=p.softmax_scale, causal=True)
+        close(out[:, hq_i:hq_i + 1], want)

@@ -1,0 +1,219 @@
+"""GPU parity of the bandwidth-bound operators against the CPU oracle, through the C ABI.
+
+Bit-exact where the op moves bytes or picks indices (store_kvcache, embedding, sampler,
+rotary); within 2e-2 abs / 1e-2 rel in 16-bit and 1e-5 in fp32 for the normalisations."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from nano_vllm_ninetoothed_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL = {torch.bfloat16: dict(atol=2e-2, rtol=1e-2), torch.float16: dict(atol=2e-2, rtol=1e-2),
+       torch.float32: dict(atol=1e-5, rtol=1e-5)}
+DTYPES = [torch.bfloat16, torch.float16, torch.float32]
+
+
+def close(got, want, dtype):
+    torch.testing.assert_close(got.float().cpu(), want.float(), **TOL[dtype])
+
+
+# ------------------------------------------------------------------ store_kvcache
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("strided", [False, True])
+def test_store_kvcache_bit_exact(mops, oracle, dtype, strided):
+    key, value, kc, vc, slots = W.make_store_case(seed=2, n_tokens=777, hkv=8, num_blocks=8,
+                                                  dtype=dtype, strided=strided, skip_every=5)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    oracle.store_kvcache(key, value, kc_ref, vc_ref, slots)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    src = torch.cat([key.reshape(777, -1), value.reshape(777, -1)], 1).to(DEV)   # one strided buffer
+    k_dev = src[:, :1024].view(777, 8, 128) if strided else key.to(DEV)
+    v_dev = src[:, 1024:].view(777, 8, 128) if strided else value.to(DEV)
+    assert mops.store_kvcache(k_dev, v_dev, kd, vd, slots.to(DEV)) is None
+    assert torch.equal(kd.cpu(), kc_ref) and torch.equal(vd.cpu(), vc_ref)
+    assert mops.device_status() == 0
+
+
+def test_store_kvcache_config2_shape_and_cache_view(mops, oracle):
+    """Prefill-sized scatter into per-layer views of one [2, L, NB, P, H, d] allocation, the way
+    nano-vLLM hands caches to its attention layers."""
+    lens = W.config_lens("prefill_small")
+    n = sum(lens)
+    key, value, _, _, slots = W.make_store_case(seed=0, n_tokens=n, hkv=8, num_blocks=128)
+    pool = torch.zeros(2, 2, 128, 256, 8, 128, dtype=torch.bfloat16)
+    ref = pool.clone()
+    oracle.store_kvcache(key, value, ref[0, 1], ref[1, 1], slots)
+    pool_d = pool.to(DEV)
+    mops.store_kvcache(key.to(DEV), value.to(DEV), pool_d[0, 1], pool_d[1, 1], slots.to(DEV))
+    assert torch.equal(pool_d.cpu(), ref)
+
+
+def test_store_kvcache_all_skipped_and_empty(mops):
+    kc = torch.zeros(2, 256, 2, 128, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    k = torch.randn(16, 2, 128, device=DEV).bfloat16()
+    mops.store_kvcache(k, k, kc, vc, torch.full((16,), -1, dtype=torch.int32, device=DEV))
+    assert not kc.any() and not vc.any()
+    mops.store_kvcache(k[:0], k[:0], kc, vc, torch.empty(0, dtype=torch.int32, device=DEV))
+    assert mops.device_status() == 0
+
+
+def test_store_kvcache_out_of_range_slot_is_skipped_and_flagged(mops):
+    kc = torch.zeros(1, 256, 1, 128, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    k = torch.ones(3, 1, 128, device=DEV).bfloat16()
+    mops.store_kvcache(k, k, kc, vc, torch.tensor([5, 256, -7], dtype=torch.int32, device=DEV))
+    assert mops.device_status() & 0x1
+    mops.reset_device_status()
+    assert kc[0, 5].all() and kc.sum().item() == 128.0
+
+
+# ------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_bit_exact(mops, oracle, dtype):
+    ids, table = W.make_embedding_case(seed=4, n_ids=1500, vocab=30011, hidden=1024, dtype=dtype)
+    want = oracle.embedding(ids, table)
+    got = mops.embedding(ids.to(DEV), table.to(DEV))
+    assert got.dtype == dtype and torch.equal(got.cpu(), want)
+
+
+def test_embedding_2d_ids_odd_hidden_and_int32(mops, oracle):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(100, 36, generator=g).bfloat16()      # 72-byte rows: unaligned path
+    ids = torch.randint(0, 100, (3, 7), generator=g)
+    got = mops.embedding(ids.to(DEV).int(), table.to(DEV))
+    assert got.shape == (3, 7, 36) and torch.equal(got.cpu(), oracle.embedding(ids, table))
+
+
+def test_embedding_full_vocab_table(mops):
+    """Config-2 sized table (151936 x 1024); the result is checked by gathering on the device."""
+    ids, table = W.make_embedding_case(seed=0, n_ids=8115, device=DEV)
+    got = mops.embedding(ids, table)
+    assert torch.equal(got, table[ids])
+    assert torch.equal(got[0], table[0]) and torch.equal(got[1], table[-1])
+
+
+def test_embedding_bad_id_gives_zero_row_and_flag(mops):
+    table = torch.ones(10, 64, dtype=torch.bfloat16, device=DEV)
+    got = mops.embedding(torch.tensor([1, 10, -1], device=DEV), table)
+    assert mops.device_status() & 0x2
+    mops.reset_device_status()
+    assert got[0].all() and not got[1:].any()
+
+
+# ------------------------------------------------------------------ RMSNorm
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [128, 1024, 4096, 1000, 8192])
+def test_add_rms_forward(mops, oracle, dtype, hidden):
+    x, r, w = W.make_rms_case(seed=7, rows=301, hidden=hidden, dtype=dtype)
+    want, want_res = oracle.add_rms_forward(x, r, w, 1e-6)
+    got, got_res = mops.add_rms_forward(x.to(DEV), r.to(DEV), w.to(DEV), 1e-6)
+    close(got, want, dtype)
+    if dtype == torch.float32:
+        # For fp32 the reference returns the normalised tensor twice (its residual aliases
+        # the buffer it later scales in place); this backend returns the true sum.
+        close(got_res, x + r, dtype)
+    else:
+        assert torch.equal(got_res.cpu(), want_res)       # cast(f32(x) + f32(r)) is exact
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rms_forward_dense_and_strided_head_views(mops, oracle, dtype):
+    g = torch.Generator().manual_seed(11)
+    qkv = torch.randn(211, (16 + 2 * 8) * 128, generator=g).to(dtype)
+    w = (1 + 0.02 * torch.randn(128, generator=g)).to(dtype)
+    qkv_d = qkv.to(DEV)
+    for lo, heads in ((0, 16), (16 * 128, 8)):
+        view = qkv[:, lo:lo + heads * 128].view(211, heads, 128)
+        view_d = qkv_d[:, lo:lo + heads * 128].view(211, heads, 128)
+        got = mops.rms_forward(view_d, w.to(DEV), 1e-6)
+        assert got.is_contiguous() and got.shape == view.shape
+        close(got, oracle.rms_forward(view, w, 1e-6), dtype)
+    x, _, w2 = W.make_rms_case(seed=8, rows=64, hidden=1024, dtype=dtype)
+    close(mops.rms_forward(x.to(DEV), w2.to(DEV), 1e-6), oracle.rms_forward(x, w2, 1e-6), dtype)
+
+
+def test_add_rms_forward_config2_size(mops, oracle):
+    rows = sum(W.config_lens("prefill_small"))
+    x, r, w = W.make_rms_case(seed=0, rows=rows, hidden=1024)
+    want, want_res = oracle.add_rms_forward(x, r, w, 1e-6)
+    got, got_res = mops.add_rms_forward(x.to(DEV), r.to(DEV), w.to(DEV), 1e-6)
+    close(got, want, torch.bfloat16)
+    assert torch.equal(got_res.cpu(), want_res)
+    # rounding differences against the oracle are confined to single bf16 ulps
+    mismatch = (got.cpu() != want).float().mean().item()
+    assert mismatch < 0.02
+
+
+# ------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_and_mul_on_strided_halves(mops, oracle, dtype):
+    g = torch.Generator().manual_seed(13)
+    gate_up = (3 * torch.randn(97, 2 * 3072, generator=g)).to(dtype)
+    a, b = gate_up.chunk(2, -1)
+    ad, bd = gate_up.to(DEV).chunk(2, -1)
+    close(mops.siluAndMul(ad, bd), oracle.siluAndMul(a, b), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_apply_rotary_emb_bit_exact(mops, oracle, dtype):
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(150, 6, 128, generator=g).to(dtype)
+    pos = torch.randint(0, 4096, (150,), generator=g)
+    inv_freq = 1.0 / (1000000.0 ** (torch.arange(0, 128, 2, dtype=torch.float) / 128))
+    freqs = torch.einsum("i,j->ij", torch.arange(4096, dtype=torch.float), inv_freq)
+    cache = torch.cat((freqs.cos(), freqs.sin()), dim=-1).unsqueeze(1)
+    cos, sin = cache[pos].chunk(2, dim=-1)
+    cos_d, sin_d = cache.to(DEV)[pos.to(DEV)].chunk(2, dim=-1)
+    got = mops.apply_rotary_emb(x.to(DEV), cos_d, sin_d)
+    assert torch.equal(got.cpu(), oracle.apply_rotary_emb(x, cos, sin))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,vocab", [(1, 151936), (9, 15193), (300, 4099), (512, 32000)])
+def test_sampler_forward_exact_with_ties(mops, oracle, dtype, rows, vocab):
+    g = torch.Generator().manual_seed(19)
+    logits = torch.randn(rows, vocab, generator=g).to(dtype)
+    top = logits.max(dim=1).values
+    logits[:, vocab // 3] = top          # exact ties: the lowest index must win
+    logits[:, vocab - 1] = top
+    temps = torch.rand(rows, generator=g) + 0.3
+    want = oracle.sampler_forward(logits, temps)
+    got = mops.sampler_forward(logits.to(DEV), temps.to(DEV))
+    assert got.dtype == torch.int64 and torch.equal(got.cpu(), want)
+
+
+# ------------------------------------------------------------------ reference-recorded outputs
+def test_against_recorded_reference_outputs(mops):
+    """The same seeded cases whose outputs were recorded from the reference's torch backend."""
+    from tests.test_oracle_golden import INPUTS, MG, RECORD
+    exact = {"embedding", "sampler_forward", "apply_rotary_emb"}
+    for name, kw in INPUTS.items():
+        digests = {k: MG.tensor_digest(v) for k, v in kw.items() if isinstance(v, torch.Tensor)}
+        if digests != RECORD["input_digests"][name]:
+            pytest.skip("torch's CPU random stream differs from the fixture's")
+        op, dt_name = name.split("/")
+        dtype = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dt_name]
+        fn = getattr(mops, {"rms_forward_qnorm": "rms_forward"}.get(op, op))
+        if op == "rms_forward_qnorm":      # rebuild the strided view on the device
+            base = kw["x"]._base.to(DEV)
+            dev_kw = dict(kw, x=base[:, : 4 * 128].view(19, 4, 128), weight=kw["weight"].to(DEV))
+        elif op == "siluAndMul":
+            a, b = kw["x"]._base.to(DEV).chunk(2, -1)
+            dev_kw = dict(x=a, y=b)
+        else:
+            dev_kw = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in kw.items()}
+        got = fn(**dev_kw)
+        got = got if isinstance(got, tuple) else (got,)
+        want = RECORD["outputs"][name]
+        if op == "add_rms_forward" and dtype == torch.float32:
+            got, want = got[:1], want[:1]      # see test_add_rms_forward on the fp32 residual
+        for g_t, w_t in zip(got, want):
+            if op in exact:
+                assert torch.equal(g_t.cpu(), w_t), name
+            else:
+                close(g_t, w_t, dtype)

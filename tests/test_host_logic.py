@@ -1,0 +1,172 @@
+"""Host-side logic that needs no GPU: the operator surface, workload generators, byte/flop
+accounting, KV-head sharding (including a 2-rank gloo run)."""
+from __future__ import annotations
+
+import inspect
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from nano_vllm_ninetoothed_b200 import workloads as W
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_mops_surface_matches_reference_names_and_call_patterns(built_library):
+    from nano_vllm_ninetoothed_b200 import mops
+    # the eleven names the reference binds at import (mops/__init__.py:15-26)
+    for name in ("linear", "rms_forward", "add_rms_forward", "softmax", "siluAndMul",
+                 "sampler_forward", "apply_rotary_emb", "embedding", "store_kvcache",
+                 "flash_attn_varlen_func", "flash_attn_with_kvcache"):
+        assert hasattr(mops, name), name
+    assert mops.softmax is None     # as in the reference's torch backend
+    sig = inspect.signature
+    # positional/keyword patterns used by nanovllm/layers/*
+    sig(mops.store_kvcache).bind("k", "v", "kc", "vc", "slots")
+    sig(mops.flash_attn_varlen_func).bind("q", "k", "v", max_seqlen_q=1, cu_seqlens_q=0,
+                                          max_seqlen_k=1, cu_seqlens_k=0, softmax_scale=1.0,
+                                          causal=True, block_table=None)
+    sig(mops.flash_attn_with_kvcache).bind("q", "kc", "vc", cache_seqlens=0, block_table=0,
+                                           softmax_scale=1.0, causal=True)
+    sig(mops.rms_forward).bind("x", "w", 1e-6)
+    sig(mops.add_rms_forward).bind("x", "r", "w", 1e-6)
+    sig(mops.embedding).bind("x", "w")
+    sig(mops.linear).bind("x", "w", None)
+    sig(mops.linear).bind("x", "w")
+    sig(mops.siluAndMul).bind("x", "y")
+    sig(mops.apply_rotary_emb).bind("x", "cos", "sin")
+    sig(mops.sampler_forward).bind("logits", "temps")
+
+
+def test_cpu_tensors_are_rejected_not_emulated(built_library):
+    from nano_vllm_ninetoothed_b200 import mops
+    x = torch.zeros(4, 128, dtype=torch.bfloat16)
+    w = torch.ones(128, dtype=torch.bfloat16)
+    for call in (lambda: mops.rms_forward(x, w, 1e-6),
+                 lambda: mops.add_rms_forward(x, x, w, 1e-6),
+                 lambda: mops.embedding(torch.zeros(2, dtype=torch.long), x),
+                 lambda: mops.siluAndMul(x, x),
+                 lambda: mops.linear(x, x)):
+        with pytest.raises(RuntimeError, match="CUDA"):
+            call()
+
+
+def test_install_as_mops_aliases_the_package(built_library):
+    import nano_vllm_ninetoothed_b200 as pkg
+    saved = sys.modules.pop("mops", None)
+    try:
+        pkg.install_as_mops()
+        import mops
+        assert mops is pkg.mops
+        from mops import store_kvcache, flash_attn_with_kvcache  # noqa: F401
+    finally:
+        sys.modules.pop("mops", None)
+        if saved is not None:
+            sys.modules["mops"] = saved
+
+
+def test_decode_case_layout_follows_the_engine():
+    c = W.make_decode_case(seed=0, batch=8, num_blocks=64)
+    assert c.q.shape == (8, 1, 16, 128) and c.k_cache.shape == (64, 256, 8, 128)
+    assert c.cache_seqlens.dtype == torch.int32 and c.block_table.dtype == torch.int32
+    used = []
+    for b in range(8):
+        n = (int(c.cache_seqlens[b]) + 255) // 256
+        row = c.block_table[b]
+        assert (row[:n] >= 0).all() and (row[n:] == -1).all()
+        used += row[:n].tolist()
+    assert len(set(used)) == len(used), "a physical block is shared by two sequences"
+    again = W.make_decode_case(seed=0, batch=8, num_blocks=64)
+    assert torch.equal(again.k_cache, c.k_cache) and torch.equal(again.block_table, c.block_table)
+
+
+def test_poisoned_case_has_nan_only_in_dead_slots():
+    c = W.make_decode_case(seed=1, lens=[1, 256, 300], hq=4, hkv=2, poison=True)
+    for b, n in enumerate([1, 256, 300]):
+        for i in range((n + 255) // 256):
+            page = c.k_cache[int(c.block_table[b, i])]
+            live = min(256, n - i * 256)
+            assert torch.isfinite(page[:live]).all() and torch.isnan(page[live:]).all()
+
+
+def test_algorithmic_byte_and_flop_formulas():
+    lens = torch.tensor([100, 256, 257], dtype=torch.int32)
+    kv = (100 + 256 + 257) * 8 * 128 * 2 * 2
+    qo = 2 * 3 * 16 * 128 * 2
+    idx = 4 * 3 + 4 * (1 + 1 + 2)
+    assert W.decode_bytes(lens, 16, 8, 128, 256) == kv + qo + idx
+    assert W.prefill_flops([3], 2, 128) == 4 * 128 * 2 * 6
+    assert W.store_bytes(10, 8, 128) == 10 * 8196
+    assert W.add_rms_bytes(10, 1024) == 10 * 1024 * 2 * 4 + 2048
+    assert W.embedding_bytes(10, 1024) == 10 * (4096 + 8)
+    # expected sizes of the named configurations
+    assert 4.3e9 < W.decode_bytes(torch.tensor(W.config_lens("decode_8b")), 32, 8, 128, 256) < 4.8e9
+    assert 0.6e12 < W.prefill_flops(W.config_lens("prefill_8b"), 32, 128) < 1.0e12
+
+
+def test_kv_head_sharding_ranges():
+    assert [W.kv_head_range(8, r, 4) for r in range(4)] == [(0, 2), (2, 4), (4, 6), (6, 8)]
+    assert W.kv_head_range(8, 7, 8) == (7, 8)
+    with pytest.raises(ValueError):
+        W.kv_head_range(8, 0, 3)
+    with pytest.raises(ValueError):
+        W.kv_head_range(8, 2, 2)
+    c = W.make_decode_case(seed=2, lens=[70, 10], hq=8, hkv=4, page=64)
+    s = W.shard_decode_case(c, 1, 2)
+    assert s.hq == 4 and s.hkv == 2
+    assert torch.equal(s.q, c.q[:, :, 4:8]) and torch.equal(s.k_cache, c.k_cache[:, :, 2:4])
+    assert s.block_table is c.block_table and s.cache_seqlens is c.cache_seqlens
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _sharded_decode_worker(rank: int, world: int, port: int):
+    """Each rank runs the oracle on its KV-head shard; concatenating the shards along the head
+    dim must reproduce the unsharded result -- the op needs no collective of its own."""
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import mops_oracle as O
+        case = W.make_decode_case(seed=5, lens=[130, 64, 1], hq=8, hkv=4, page=64)
+        shard = W.shard_decode_case(case, rank, world)
+        mine = O.flash_attn_with_kvcache(shard.q, shard.k_cache, shard.v_cache,
+                                         cache_seqlens=shard.cache_seqlens,
+                                         block_table=shard.block_table,
+                                         softmax_scale=shard.softmax_scale).float()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        full = O.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                         cache_seqlens=case.cache_seqlens,
+                                         block_table=case.block_table,
+                                         softmax_scale=case.softmax_scale).float()
+        assert torch.equal(torch.cat(parts, dim=2), full)
+        # the bench's aggregate: units summed over ranks, time = max over ranks
+        t = torch.tensor([1.0 + rank])
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        assert t.item() == float(world)
+        p = W.make_prefill_case(seed=6, lens=[40, 9], hq=4, hkv=2)
+        ps = W.shard_prefill_case(p, rank, world)
+        mine_p = O.flash_attn_varlen_func(ps.q, ps.k, ps.v, ps.cu_seqlens, ps.cu_seqlens, 40, 40,
+                                          softmax_scale=ps.softmax_scale, causal=True).float()
+        parts_p = [torch.empty_like(mine_p) for _ in range(world)]
+        dist.all_gather(parts_p, mine_p)
+        full_p = O.flash_attn_varlen_func(p.q, p.k, p.v, p.cu_seqlens, p.cu_seqlens, 40, 40,
+                                          softmax_scale=p.softmax_scale, causal=True).float()
+        assert torch.equal(torch.cat(parts_p, dim=1), full_p)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_kv_head_sharding_two_ranks_gloo():
+    mp.spawn(_sharded_decode_worker, args=(2, _free_port()), nprocs=2, join=True)

@@ -1,0 +1,128 @@
+"""The CPU oracle against outputs recorded from the reference's own torch backend, and
+against itself where two of its functions must agree.  No GPU needed."""
+from __future__ import annotations
+
+import importlib.util
+from pathlib import Path
+
+import pytest
+import torch
+
+from oracle import mops_oracle as O
+
+GOLDEN_DIR = Path(__file__).resolve().parent / "golden"
+
+
+def _load_make_golden():
+    spec = importlib.util.spec_from_file_location("make_golden", GOLDEN_DIR / "make_golden.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+MG = _load_make_golden()
+RECORD = torch.load(GOLDEN_DIR / "torch_backend.pt")
+INPUTS = MG.golden_inputs()
+
+
+@pytest.mark.parametrize("name", sorted(RECORD["outputs"]))
+def test_oracle_reproduces_reference_torch_backend(name):
+    kw = INPUTS[name]
+    digests = {k: MG.tensor_digest(v) for k, v in kw.items() if isinstance(v, torch.Tensor)}
+    if digests != RECORD["input_digests"][name]:
+        pytest.skip("torch's CPU random stream differs from the one the fixture was made with")
+    got = MG.call_case(O, name, kw)
+    want = RECORD["outputs"][name]
+    got = got if isinstance(got, tuple) else (got,)
+    assert len(got) == len(want)
+    for g, w in zip(got, want):
+        assert g.dtype == w.dtype and g.shape == w.shape
+        assert torch.equal(g, w), f"{name}: oracle differs from the reference output"
+
+
+def test_sampler_tie_goes_to_lowest_index():
+    out = RECORD["outputs"]["sampler_forward/bf16"][0]
+    assert int(out[3]) == 100
+
+
+def _decode_by_token_loop(q, k_cache, v_cache, lens, table, scale):
+    """Token-by-token gather exactly as the reference's commented pure-torch decode spells it
+    out (mops/torch/ops.py:78-125), for tiny cases only."""
+    o = torch.empty_like(q)
+    page = k_cache.shape[1]
+    for b in range(q.shape[0]):
+        n = int(lens[b])
+        k = torch.empty((1, n, k_cache.shape[2], q.shape[3]), dtype=q.dtype)
+        v = torch.empty_like(k)
+        for i in range(n):
+            k[0, i] = k_cache[table[b, i // page], i % page]
+            v[0, i] = v_cache[table[b, i // page], i % page]
+        rep = q.shape[2] // k.shape[2]
+        k = k.unsqueeze(-2).expand(-1, -1, -1, rep, -1).reshape(1, n, q.shape[2], q.shape[3])
+        v = v.unsqueeze(-2).expand(-1, -1, -1, rep, -1).reshape(1, n, q.shape[2], q.shape[3])
+        qb = q[[b]].permute(0, 2, 1, 3).float()
+        ob = torch.nn.functional.scaled_dot_product_attention(
+            qb, k.permute(0, 2, 1, 3).float(), v.permute(0, 2, 1, 3).float(), scale=scale,
+            is_causal=False)
+        o[[b]] = ob.permute(0, 2, 1, 3).to(q.dtype)
+    return o
+
+
+def test_decode_oracle_matches_token_loop_statement():
+    from nano_vllm_ninetoothed_b200.workloads import make_decode_case
+    c = make_decode_case(seed=3, lens=[1, 63, 64, 65, 130], hq=4, hkv=2, page=64)
+    want = _decode_by_token_loop(c.q, c.k_cache, c.v_cache, c.cache_seqlens, c.block_table,
+                                 c.softmax_scale)
+    got = O.flash_attn_with_kvcache(c.q, c.k_cache, c.v_cache, cache_seqlens=c.cache_seqlens,
+                                    block_table=c.block_table, softmax_scale=c.softmax_scale,
+                                    causal=True)
+    torch.testing.assert_close(got.float(), want.float(), atol=1e-2, rtol=1e-2)
+
+
+def test_prefill_oracle_last_row_equals_decode_oracle():
+    """The last query row of a causal prefill is a decode step over the same keys."""
+    from nano_vllm_ninetoothed_b200.workloads import make_prefill_case
+    p = make_prefill_case(seed=5, lens=[70, 129], hq=4, hkv=2)
+    full = O.flash_attn_varlen_func(p.q, p.k, p.v, p.cu_seqlens, p.cu_seqlens, p.max_seqlen,
+                                    p.max_seqlen, softmax_scale=p.softmax_scale, causal=True)
+    page = 64
+    for b, n in enumerate(p.lens):
+        s = int(p.cu_seqlens[b])
+        nblk = (n + page - 1) // page
+        kc = torch.zeros(nblk, page, 2, 128, dtype=p.k.dtype)
+        vc = torch.zeros_like(kc)
+        kc.view(-1, 2, 128)[:n] = p.k[s:s + n]
+        vc.view(-1, 2, 128)[:n] = p.v[s:s + n]
+        q = p.q[s + n - 1].view(1, 1, 4, 128)
+        dec = O.flash_attn_with_kvcache(q, kc, vc, cache_seqlens=torch.tensor([n], dtype=torch.int32),
+                                        block_table=torch.arange(nblk, dtype=torch.int32).view(1, -1),
+                                        softmax_scale=p.softmax_scale)
+        torch.testing.assert_close(dec[0, 0].float(), full[s + n - 1].float(), atol=1e-2, rtol=1e-2)
+
+
+def test_prefill_oracle_bottom_right_alignment():
+    """With a cached prefix, query i of the new tokens sees keys up to prefix + i."""
+    from nano_vllm_ninetoothed_b200.workloads import make_prefill_case
+    p = make_prefill_case(seed=6, lens=[96], hq=2, hkv=1)
+    full = O.flash_attn_varlen_func(p.q, p.k, p.v, p.cu_seqlens, p.cu_seqlens, 96, 96,
+                                    softmax_scale=p.softmax_scale, causal=True)
+    cu_q = torch.tensor([0, 32], dtype=torch.int32)
+    part = O.flash_attn_varlen_func(p.q[64:], p.k, p.v, cu_q, p.cu_seqlens, 32, 96,
+                                    softmax_scale=p.softmax_scale, causal=True)
+    assert torch.equal(part, full[64:])
+
+
+def test_store_kvcache_oracle_skips_minus_one_and_is_exact():
+    from nano_vllm_ninetoothed_b200.workloads import make_store_case
+    key, value, kc, vc, slots = make_store_case(seed=1, n_tokens=50, hkv=2, num_blocks=2, page=64,
+                                                skip_every=7)
+    O.store_kvcache(key, value, kc, vc, slots)
+    flat_k, flat_v = kc.view(-1, 256), vc.view(-1, 256)
+    written = torch.zeros(128, dtype=torch.bool)
+    for i, s in enumerate(slots.tolist()):
+        if s == -1:
+            continue
+        written[s] = True
+        assert torch.equal(flat_k[s], key[i].reshape(-1))
+        assert torch.equal(flat_v[s], value[i].reshape(-1))
+    assert not flat_k[~written].any() and not flat_v[~written].any()
