@@ -56,53 +56,70 @@ def peaks() -> dict:
 
 
 class ClockSampler:
-    """nvidia-smi clock/throttle samples taken while the timed region runs (read-only)."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """nvidia-smi clock/throttle samples (read-only queries) taken while the load runs.
+
+    The sampler is started before the warm-up so that it is already ticking when the timed
+    region begins; `mark()` brackets the region by wall clock and only samples inside the
+    marks are summarised.  When the region is too short to catch three samples, the caller
+    keeps the same load running a little longer inside a second pair of marks."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.proc = None
-
-    def __enter__(self):
+        self.marks: list[float] = []
+        self.lines: list[str] = []
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu_index), "-lms", "50"],
+                 "-i", str(gpu_index), "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.proc.stdout.readline()          # first sample: the tool is up
         except OSError:
             self.proc = None
-        return self
 
-    def __exit__(self, *exc):
-        self.lines = []
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                out, _ = self.proc.communicate(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
-                out, _ = self.proc.communicate()
-            self.lines = [l for l in out.splitlines() if l.strip()]
+    def mark(self) -> None:
+        self.marks.append(time.time())
+
+    def stop(self) -> None:
+        if self.proc is None:
+            return
+        time.sleep(0.05)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        self.lines = [l for l in out.splitlines() if l.strip()]
+        self.proc = None
 
     def summary(self) -> dict:
-        sm, smax, reasons = [], 0.0, set()
+        from datetime import datetime
+        windows = list(zip(self.marks[0::2], self.marks[1::2]))
+        sm, smax, reasons, total = [], 0.0, set(), 0
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             f = [x.strip() for x in line.split(",")]
-            if len(f) < 8:
+            if len(f) < 7:
                 continue
             try:
-                sm.append(float(f[1]))
-                smax = max(smax, float(f[2]))
+                ts = datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk, cmax = float(f[1]), float(f[2])
             except ValueError:
                 continue
-            for name, val in zip(names, f[4:8]):
+            total += 1
+            if not any(a - 0.005 <= ts <= b + 0.005 for a, b in windows):
+                continue
+            sm.append(clk)
+            smax = max(smax, cmax)
+            for name, val in zip(names, f[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax or None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "samples_total": total,
+                "window": "timed region" if len(windows) == 1 else
+                          "timed region + 0.5 s more of the same load"}
 
 
 def dist_env():
@@ -112,7 +129,7 @@ def dist_env():
     return rank, world, local
 
 
-def timed_steps(fn, steps: int, warmup: int, world: int, sampler: ClockSampler | None):
+def timed_steps(fn, steps: int, warmup: int, world: int, sampler: ClockSampler | None = None):
     """W untimed calls, then K calls between two events; returns max-over-ranks milliseconds."""
     import torch.distributed as dist
     for _ in range(warmup):
@@ -122,28 +139,48 @@ def timed_steps(fn, steps: int, warmup: int, world: int, sampler: ClockSampler |
         dist.barrier()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ctx = sampler if sampler is not None else _Null()
-    with ctx:
-        start.record()
-        for _ in range(steps):
-            fn()
-        stop.record()
-        torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.mark()
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.mark()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device="cuda")
+    local_ms = start.elapsed_time(stop)
+    if sampler is not None and local_ms < 150.0:
+        # too short for three 20 ms samples: keep the identical load up for half a second
+        sampler.mark()
+        t_end = time.time() + 0.5
+        while time.time() < t_end:
+            for _ in range(steps):
+                fn()
+            torch.cuda.synchronize()
+        sampler.mark()
+    ms = torch.tensor([local_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     return float(ms.item())
 
 
-class _Null:
-    def __enter__(self):
-        return self
-
-    def __exit__(self, *exc):
-        return False
+def graph_of(fn_list):
+    """Capture a sequence of op calls in one CUDA graph (host launch cost out of the picture)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for f in fn_list:          # warm-up outside capture: lazy set-up, allocator pools
+            f()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fn_list:
+            f()
+    return g
 
 
 def cpu_baseline_decode(lens: list[int], budget_s: float = 12.0) -> dict:
@@ -217,7 +254,7 @@ def bench_side_ops(mops, dev, rank: int, world: int, steps: int, warmup: int, pk
                                              cu_seqlens_q=p.cu_seqlens, max_seqlen_k=p.max_seqlen,
                                              cu_seqlens_k=p.cu_seqlens,
                                              softmax_scale=p.softmax_scale, causal=True)
-    ms = timed_steps(fn, steps, warmup, world, None) / steps
+    ms = timed_steps(fn, steps, warmup, world) / steps
     flops = W.prefill_flops(lens, HQ, HEAD_DIM)
     tf = flops / (ms * 1e-3) / 1e12
     out["varlen_prefill"] = {"workload": "Qwen3-8B heads, 16 seqs U[256,4096], causal, bf16",
@@ -226,29 +263,34 @@ def bench_side_ops(mops, dev, rank: int, world: int, steps: int, warmup: int, pk
     del p
     if world > 1:
         return out
-    # prefill-side bandwidth ops at Qwen3-0.6B shapes (T ~ 8.1k tokens); six input sets rotate
+    # prefill-side bandwidth ops at Qwen3-0.6B shapes (T ~ 8.1k tokens).  Six independent input
+    # sets (together larger than L2) are visited in turn; the six calls are replayed as one CUDA
+    # graph so that the figure is the kernels' and not the Python launch path's.
     t = sum(W.config_lens("prefill_small"))
-    step = rotate(lambda i: W.make_store_case(seed=i, n_tokens=t, hkv=8, num_blocks=128, device=dev), 6)
-    ms = timed_steps(step(lambda k, v, kc, vc, s: mops.store_kvcache(k, v, kc, vc, s)), steps * 6,
-                     warmup, 1, None) / (steps * 6)
+    n_sets = 6
+
+    def per_call_ms(calls):
+        g = graph_of(calls)
+        return timed_steps(g.replay, steps, warmup, 1) / (steps * len(calls))
+
+    sets = [W.make_store_case(seed=i, n_tokens=t, hkv=8, num_blocks=128, device=dev) for i in range(n_sets)]
+    ms = per_call_ms([(lambda a=a: mops.store_kvcache(*a)) for a in sets])
     gbs = W.store_bytes(t, 8, 128) / (ms * 1e-3) / 1e9
     out["store_kvcache"] = {"tokens": t, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
-    step = rotate(lambda i: W.make_rms_case(seed=i, rows=t, hidden=1024, device=dev), 6)
-    ms = timed_steps(step(lambda x, r, w: mops.add_rms_forward(x, r, w, 1e-6)), steps * 6,
-                     warmup, 1, None) / (steps * 6)
+    del sets
+    sets = [W.make_rms_case(seed=i, rows=t, hidden=1024, device=dev) for i in range(n_sets)]
+    ms = per_call_ms([(lambda a=a: mops.add_rms_forward(a[0], a[1], a[2], 1e-6)) for a in sets])
     gbs = W.add_rms_bytes(t, 1024) / (ms * 1e-3) / 1e9
     out["add_rms_forward"] = {"rows": t, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
-    ids0, table = W.make_embedding_case(seed=0, n_ids=t, device=dev)
+    del sets
+    _, table = W.make_embedding_case(seed=0, n_ids=t, device=dev)
     g = torch.Generator().manual_seed(3)
-    id_sets = [torch.randint(0, 151936, (t,), generator=g).to(dev) for _ in range(6)]
-    state = {"i": 0}
-
-    def emb():
-        mops.embedding(id_sets[state["i"] % 6], table)
-        state["i"] += 1
-    ms = timed_steps(emb, steps * 6, warmup, 1, None) / (steps * 6)
+    id_sets = [torch.randint(0, 151936, (t,), generator=g).to(dev) for _ in range(n_sets)]
+    ms = per_call_ms([(lambda ids=ids: mops.embedding(ids, table)) for ids in id_sets])
     gbs = W.embedding_bytes(t, 1024) / (ms * 1e-3) / 1e9
-    out["embedding"] = {"ids": t, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
+    out["embedding"] = {"ids": t, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"],
+                        "note": "311 MB table, random rows; six id sets"}
+    out["timing"] = "CUDA-graph replay of six calls on six input sets, events around the replays"
     return out
 
 
@@ -286,7 +328,10 @@ def run_ours(args) -> None:
     total_ms = timed_steps(step, args.steps, args.warmup, world, sampler)
     ms_step = total_ms / args.steps
     value = bytes_total / (ms_step * 1e-3) / 1e9
-    clocks = sampler.summary() if sampler is not None else {}
+    clocks = {}
+    if sampler is not None:
+        sampler.stop()
+        clocks = sampler.summary()
 
     # end to end through the public op with host buffers: every step copies q, the lengths and
     # the block table from pinned host memory and reads the output back.  The K/V pool is the
@@ -305,7 +350,7 @@ def run_ours(args) -> None:
                                          causal=True)
         o_h.copy_(o, non_blocking=True)
 
-    e2e_ms = timed_steps(e2e_step, args.steps, args.warmup, world, None) / args.steps
+    e2e_ms = timed_steps(e2e_step, args.steps, args.warmup, world) / args.steps
     h2d = q_h.numel() * 2 + lens_h.numel() * 4 + tbl_h.numel() * 4
     d2h = o_h.numel() * 2
     e2e_value = bytes_total / (e2e_ms * 1e-3) / 1e9

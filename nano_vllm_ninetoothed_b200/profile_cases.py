@@ -1,0 +1,75 @@
+"""Run one operator a few times on a bounded, seeded case -- the target of profiler captures.
+
+    python -m nano_vllm_ninetoothed_b200.profile_cases decode  [--seqs 64] [--iters 3]
+    python -m nano_vllm_ninetoothed_b200.profile_cases prefill [--seqs 4]
+    python -m nano_vllm_ninetoothed_b200.profile_cases store | add_rms | embedding
+
+The decode and prefill cases use the head shapes and length distributions of the large
+benchmark configurations with fewer sequences, so that the K/V footprint stays far above L2
+but within a couple of GB.  Prints the CUDA-event time of each iteration.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import mops
+from . import workloads as W
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["decode", "prefill", "store", "add_rms", "embedding"])
+    ap.add_argument("--seqs", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--hkv", type=int, default=8)
+    ap.add_argument("--chunk", type=int, default=0)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = 4
+    if a.op == "decode":
+        lens = W.config_lens("decode_8b")[: a.seqs or 64]
+        c = W.make_decode_case(seed=0, lens=lens, hq=a.hkv * g, hkv=a.hkv, device=dev, cache_on_device=True)
+        units, unit = c.algorithmic_bytes() / 1e9, "GB"
+        fn = lambda: mops.flash_attn_with_kvcache(c.q, c.k_cache, c.v_cache, cache_seqlens=c.cache_seqlens,
+                                                  block_table=c.block_table, softmax_scale=c.softmax_scale,
+                                                  causal=True, chunk_tokens=a.chunk)
+    elif a.op == "prefill":
+        lens = W.config_lens("prefill_8b")[: a.seqs or 4]
+        p = W.make_prefill_case(seed=0, lens=lens, hq=a.hkv * g, hkv=a.hkv, device=dev)
+        units, unit = p.flops() / 1e12, "TFLOP"
+        fn = lambda: mops.flash_attn_varlen_func(p.q, p.k, p.v, max_seqlen_q=p.max_seqlen,
+                                                 cu_seqlens_q=p.cu_seqlens, max_seqlen_k=p.max_seqlen,
+                                                 cu_seqlens_k=p.cu_seqlens, softmax_scale=p.softmax_scale,
+                                                 causal=True)
+    else:
+        t = 8 * sum(W.config_lens("prefill_small"))     # ~65k tokens: footprint well above L2
+        if a.op == "store":
+            args = W.make_store_case(seed=0, n_tokens=t, hkv=8, num_blocks=1024, device=dev)
+            units, unit = W.store_bytes(t, 8, 128) / 1e9, "GB"
+            fn = lambda: mops.store_kvcache(*args)
+        elif a.op == "add_rms":
+            x, r, w = W.make_rms_case(seed=0, rows=t, hidden=1024, device=dev)
+            units, unit = W.add_rms_bytes(t, 1024) / 1e9, "GB"
+            fn = lambda: mops.add_rms_forward(x, r, w, 1e-6)
+        else:
+            ids, table = W.make_embedding_case(seed=0, n_ids=t, device=dev)
+            units, unit = W.embedding_bytes(t, 1024) / 1e9, "GB"
+            fn = lambda: mops.embedding(ids, table)
+    fn()
+    torch.cuda.synchronize()
+    for i in range(a.iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        print(f"{a.op} iter {i}: {ms:.4f} ms, {units:.4f} {unit} -> {units / (ms * 1e-3):.1f} {unit}/s")
+    assert mops.device_status() == 0
+
+
+if __name__ == "__main__":
+    main()
