@@ -203,6 +203,24 @@ int32_t b200mops_paged_decode_auto_chunk(int64_t batch, int64_t hkv, int64_t pag
 int b200mops_paged_decode(const b200mops_paged_decode_args* args, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Paged decode without a caller-supplied workspace -- this entry point has no counterpart in
+ * the reference.  It is for callers that cannot allocate device memory when they call: an
+ * engine whose memory was handed out and frozen at start-up, or a host framework that forbids
+ * allocation on the calling thread.  The split-K partials live in a fixed array inside the
+ * library (B200MOPS_PAGED_DECODE_STATIC_SCRATCH_BYTES on every GPU that loads it, held until
+ * the process exits); `workspace` / `workspace_bytes` in `args` are ignored, everything else
+ * means what it means for b200mops_paged_decode, and the results are the same.
+ * Returns B200MOPS_ERR_TOO_LARGE, launching nothing, when
+ * b200mops_paged_decode_workspace_bytes(...) for these sizes exceeds the fixed capacity
+ * (shrink the batch, or raise chunk_tokens).  The call itself allocates nothing.
+ * All calls on a device share the one array: order them on a stream; calls that overlap on
+ * the GPU race.  The first call on each device looks the array's address up -- make it
+ * before any stream capture begins.
+ * ---------------------------------------------------------------------- */
+#define B200MOPS_PAGED_DECODE_STATIC_SCRATCH_BYTES (16u << 20)
+int b200mops_paged_decode_static_scratch(const b200mops_paged_decode_args* args, void* stream);
+
+/* ------------------------------------------------------------------------
  * Variable-length causal prefill attention over packed tokens.
  *   per sequence b, head h: softmax(scale * Q_b K_b^T + causal mask) V_b with
  *   KV head h / G; the causal mask is aligned to the bottom-right corner

@@ -12,6 +12,8 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libb200mops.so"
 
 BF16, F16, F32 = 0, 1, 2
 
+PAGED_DECODE_STATIC_SCRATCH_BYTES = 16 << 20
+
 DEV_BAD_SLOT, DEV_BAD_TOKEN_ID, DEV_BAD_PAGE, DEV_WAIT_TIMEOUT = 0x1, 0x2, 0x4, 0x8
 
 # Every symbol the header declares; tests check that the library exports all of them.
@@ -30,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "b200mops_paged_decode_workspace_bytes",
     "b200mops_paged_decode_auto_chunk",
     "b200mops_paged_decode",
+    "b200mops_paged_decode_static_scratch",
     "b200mops_varlen_prefill",
 )
 
@@ -87,6 +90,7 @@ _SIGNATURES = {
     "b200mops_paged_decode_workspace_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64, _i64, _i32]),
     "b200mops_paged_decode_auto_chunk": (_i32, [_i64, _i64, _i64, _i64]),
     "b200mops_paged_decode": (C.c_int, [C.POINTER(PagedDecodeArgs), _vp]),
+    "b200mops_paged_decode_static_scratch": (C.c_int, [C.POINTER(PagedDecodeArgs), _vp]),
     "b200mops_varlen_prefill": (C.c_int, [C.POINTER(VarlenPrefillArgs), _vp]),
 }
 

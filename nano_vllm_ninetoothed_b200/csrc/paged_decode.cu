@@ -472,3 +472,69 @@ extern "C" int b200mops_paged_decode(const b200mops_paged_decode_args* a, void* 
         return launch_decode<__nv_bfloat16, 3>(tm_k, tm_v, p, a->batch, a->hkv, st);
     return launch_decode<__half, 3>(tm_k, tm_v, p, a->batch, a->hkv, st);
 }
+
+// ------------------------------------------------------------------------------------------
+// Paged decode for callers that must not allocate.
+//
+// Some hosts of this library cannot obtain device memory at call time: a serving loop whose
+// memory pool was sized and frozen at start-up (nano-vLLM gives every spare byte to the KV
+// cache), a plugin running under a framework that forbids cudaMalloc on its threads, or code
+// running where a failed or slow allocation is not acceptable.  For them the split-K partials
+// go into a fixed array that is part of the library image instead of a caller-supplied buffer.
+//
+// The array costs B200MOPS_PAGED_DECODE_STATIC_SCRATCH_BYTES of device memory on every GPU
+// that loads the library, for the life of the process.  All calls on one device share it:
+// two calls whose kernels overlap on the GPU (different streams, or graphs replayed
+// concurrently) race on it and corrupt each other's result; calls ordered on one stream are
+// fine.  Nothing in it has to start at zero -- every partial that the combine step reads has
+// been written by the same call -- so it is never cleared, and it keeps the last call's bytes.
+//
+// In host code the array's name is only a handle, not a device address, so the address is
+// looked up once per device with cudaGetSymbolAddress while that device is current.  That
+// look-up happens inside the first call on each device (it may make the runtime load this
+// module); make that first call before starting any stream capture.
+namespace b200mops {
+namespace {
+
+constexpr size_t kStaticScratchBytes = B200MOPS_PAGED_DECODE_STATIC_SCRATCH_BYTES;
+constexpr int kMaxDevices = 64;
+
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+void* static_scratch_on_current_device(int* rc) {
+    static void* volatile ptrs[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        *rc = B200MOPS_ERR_DEVICE;
+        return nullptr;
+    }
+    void* p = ptrs[dev];
+    if (p == nullptr) {
+        // Racing first calls on one device compute the same address; the store is idempotent.
+        if (cudaGetSymbolAddress(&p, g_decode_static_scratch) != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            *rc = B200MOPS_ERR_LAUNCH;
+            return nullptr;
+        }
+        ptrs[dev] = p;
+    }
+    return p;
+}
+
+}  // namespace
+}  // namespace b200mops
+
+extern "C" int b200mops_paged_decode_static_scratch(const b200mops_paged_decode_args* a,
+                                                    void* stream) {
+    if (!a) return B200MOPS_ERR_NULL_POINTER;
+    const size_t need = b200mops_paged_decode_workspace_bytes(
+        a->batch, a->hq, a->hkv, a->head_dim, a->page, a->max_blocks_per_seq, a->chunk_tokens);
+    if (need > kStaticScratchBytes) return B200MOPS_ERR_TOO_LARGE;
+    int rc = B200MOPS_OK;
+    void* scratch = static_scratch_on_current_device(&rc);
+    if (!scratch) return rc;
+    b200mops_paged_decode_args with_scratch = *a;
+    with_scratch.workspace = scratch;
+    with_scratch.workspace_bytes = kStaticScratchBytes;
+    return b200mops_paged_decode(&with_scratch, stream);
+}

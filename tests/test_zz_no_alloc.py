@@ -1,0 +1,97 @@
+"""Paged decode through the entry point that brings its own scratch memory.
+
+`b200mops_paged_decode_static_scratch` exists for hosts that cannot allocate device memory at
+the moment they call: an inference engine that handed every spare byte to its KV cache at
+start-up, or a plugin whose host framework forbids allocation on the calling thread.  Its
+split-K partials go into a fixed 16 MiB array inside the library instead of a buffer that the
+caller would have to obtain.  This file is named to be collected last, calls both entry
+points through the C ABI on the same inputs, and requires the same answer twice in a row
+(the second call with other inputs, so that bytes left behind by the first cannot help).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import pytest
+import torch
+
+from nano_vllm_ninetoothed_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL = dict(atol=2e-2, rtol=1e-2)      # the attention tolerance used throughout the GPU tests
+
+
+def _args(cabi, case, out, workspace, chunk):
+    q, kc, vc = case.q, case.k_cache, case.v_cache
+    batch, _, hq, hd = q.shape
+    nb, page, hkv, _ = kc.shape
+    return cabi.PagedDecodeArgs(
+        q=q.data_ptr(), q_stride_b=q.stride(0), q_stride_h=q.stride(2),
+        out=out.data_ptr(), out_stride_b=out.stride(0), out_stride_h=out.stride(2),
+        k_cache=kc.data_ptr(), k_stride_block=kc.stride(0), k_stride_token=kc.stride(1),
+        k_stride_head=kc.stride(2),
+        v_cache=vc.data_ptr(), v_stride_block=vc.stride(0), v_stride_token=vc.stride(1),
+        v_stride_head=vc.stride(2),
+        cache_seqlens=case.cache_seqlens.data_ptr(), block_table=case.block_table.data_ptr(),
+        table_stride0=case.block_table.stride(0),
+        batch=batch, hq=hq, hkv=hkv, head_dim=hd, page=page, num_blocks=nb,
+        max_blocks_per_seq=case.block_table.shape[1], softmax_scale=case.softmax_scale,
+        chunk_tokens=chunk,
+        workspace=workspace.data_ptr() if workspace is not None else None,
+        workspace_bytes=workspace.numel() if workspace is not None else 0,
+        status_word=None, dtype=cabi.BF16)
+
+
+def _both_ways(cabi, case, chunk):
+    """(result with a caller-allocated workspace, result with the library's own scratch)."""
+    lib = cabi.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    batch, _, hq, hd = case.q.shape
+    need = lib.b200mops_paged_decode_workspace_bytes(batch, hq, case.hkv, hd, case.page,
+                                                     case.block_table.shape[1], chunk)
+    assert 0 < need <= cabi.PAGED_DECODE_STATIC_SCRATCH_BYTES, "case must exercise the scratch"
+    ws = torch.empty(need, dtype=torch.uint8, device=DEV)
+    ref = torch.full_like(case.q, float("nan"))
+    cabi.check("b200mops_paged_decode",
+               lib.b200mops_paged_decode(C.byref(_args(cabi, case, ref, ws, chunk)), stream))
+    got = torch.full_like(case.q, float("nan"))
+    # no workspace is passed: the pointer and size fields stay NULL / 0
+    cabi.check("b200mops_paged_decode_static_scratch",
+               lib.b200mops_paged_decode_static_scratch(
+                   C.byref(_args(cabi, case, got, None, chunk)), stream))
+    torch.cuda.synchronize()
+    return ref, got
+
+
+def test_static_scratch_decode_matches_the_workspace_entry_point_twice(built_library):
+    assert torch.cuda.is_available(), "GPU test selected but no CUDA device is visible"
+    from nano_vllm_ninetoothed_b200 import _cabi as cabi
+    torch.cuda.set_device(0)
+    first = W.make_decode_case(seed=21, batch=12, len_lo=1, len_hi=2000, hq=16, hkv=4,
+                               poison=True).to(DEV)
+    second = W.make_decode_case(seed=22, lens=[700, 5, 0, 1300, 256], hq=8, hkv=2,
+                                poison=True).to(DEV)
+    for case, chunk in ((first, 128), (second, 256)):
+        ref, got = _both_ways(cabi, case, chunk)
+        assert torch.isfinite(got).all()
+        torch.testing.assert_close(got.float(), ref.float(), **TOL)
+
+
+def test_static_scratch_decode_rejects_sizes_beyond_its_capacity(built_library):
+    """More partials than the fixed array holds: a clear error and no launch (the output keeps
+    its sentinel), never a silent overrun."""
+    assert torch.cuda.is_available(), "GPU test selected but no CUDA device is visible"
+    from nano_vllm_ninetoothed_b200 import _cabi as cabi
+    torch.cuda.set_device(0)
+    lens = [4096] * 64
+    case = W.make_decode_case(seed=23, lens=lens, hq=32, hkv=8, device=DEV, cache_on_device=True)
+    need = cabi.lib.b200mops_paged_decode_workspace_bytes(64, 32, 8, 128, 256, 16, 64)
+    assert need > cabi.PAGED_DECODE_STATIC_SCRATCH_BYTES
+    out = torch.full_like(case.q, 7.0)
+    rc = cabi.lib.b200mops_paged_decode_static_scratch(
+        C.byref(_args(cabi, case, out, None, 64)), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert rc == 14 and "capacity" in cabi.strerror(rc)
+    assert (out == 7.0).all()
