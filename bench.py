@@ -41,9 +41,11 @@ HQ, HKV, HEAD_DIM, PAGE = 32, 8, 128, 256
 WORKLOAD = ("paged decode attention, Qwen3-8B heads (32q/8kv, d128), 256 seqs, ctx U[512,8192], "
             "page 256, bf16")
 
-# DRAM bytes of one full-size launch of the decode kernel on one GPU, from the ncu capture
-# summarised under profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of the decode kernel divided by its algorithmic
+# bytes, from the ncu capture of a 64-sequence slice of this workload (summary under profiles/).
+# DRAM traffic grows in proportion to the live tokens, so a full launch is scaled by its
+# algorithmic bytes.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0147
 
 
 def peaks() -> dict:
@@ -372,7 +374,7 @@ def run_ours(args) -> None:
                    "kv_bytes_total": bytes_total, "chunk_tokens": chunk,
                    "l2": "inputs larger than L2 (>=570 MB of K/V per GPU per step), no flush"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": UNIT,
-                     "frac": achieved / pk["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "frac": achieved / pk["hbm_gbs"], "traffic": int(NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_rank),
                      "peak_source": pk["source"],
                      "note": "duration = one step (decode kernel + split combine kernel)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
