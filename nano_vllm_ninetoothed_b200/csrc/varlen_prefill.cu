@@ -13,7 +13,11 @@
 // configuration; the tcgen05 kernel takes over the shapes it covers.
 #include <math.h>
 
+#include <stdlib.h>
+#include <string.h>
+
 #include "attn_common.cuh"
+#include "prefill_internal.h"
 
 namespace b200mops {
 namespace {
@@ -310,6 +314,16 @@ extern "C" int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* a, vo
     if (!aligned16(a->out) || (a->out_stride_t % 8) || (a->out_stride_h % 8))
         return B200MOPS_ERR_ALIGNMENT;
 
+    // Kernel choice: the tcgen05 kernel takes packed K/V with an even number of query heads per
+    // KV head; paged K/V (prefix-cache prefill) and odd groupings stay on the mma.sync kernel.
+    // B200MOPS_PREFILL_KERNEL=mma forces the latter (for A/B measurements).
+    static const bool force_mma = [] {
+        const char* e = getenv("B200MOPS_PREFILL_KERNEL");
+        return e != nullptr && strcmp(e, "mma") == 0;
+    }();
+    const bool use_tc5 = !paged && ((a->hq / a->hkv) % 2 == 0) && !force_mma;
+    const uint32_t kv_box_rows = use_tc5 ? 128u : (uint32_t)kBN;
+
     CUtensorMap tm_q, tm_k, tm_v;
     {
         const uint64_t dims[4] = {(uint64_t)kHeadDim, (uint64_t)a->hq, (uint64_t)a->total_q, 1};
@@ -323,7 +337,7 @@ extern "C" int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* a, vo
         const uint64_t rows = paged ? (uint64_t)a->page : (uint64_t)a->total_k;
         const uint64_t blocks = paged ? (uint64_t)a->num_blocks : 1;
         const uint64_t dims[4] = {(uint64_t)kHeadDim, (uint64_t)a->hkv, rows, blocks};
-        const uint32_t box[4] = {64, 1, (uint32_t)kBN, 1};
+        const uint32_t box[4] = {64, 1, kv_box_rows, 1};
         const uint64_t ks[3] = {(uint64_t)a->k_stride_h * 2, (uint64_t)a->k_stride_t * 2,
                                 paged ? (uint64_t)a->k_stride_block * 2
                                       : (uint64_t)a->k_stride_t * 2 * rows};
@@ -337,6 +351,8 @@ extern "C" int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* a, vo
         rc = encode_map_16bit(&tm_v, a->dtype, a->v, 4, dims, vs, box);
         if (rc != B200MOPS_OK) return rc;
     }
+
+    if (use_tc5) return launch_varlen_prefill_tc5(a, tm_q, tm_k, tm_v, as_stream(stream));
 
     PrefillParams p;
     p.out = a->out; p.out_stride_t = a->out_stride_t; p.out_stride_h = a->out_stride_h;
