@@ -220,7 +220,7 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
         const float c = p.scale_log2;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        uint32_t v[32];
+        uint32_t sv[kBN / 32][32];
         for (int j = 0; j < ntiles; ++j) {
             ok = mbar_wait(bar(S_FULL + t), (uint32_t)j & 1u, p.status);
             if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
@@ -228,21 +228,29 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
             const int key0 = j * kBN;
             const bool need_mask = key0 + kBN - 1 > lim;      // this row crosses its limit here
             const bool warp_mask = __any_sync(0xffffffffu, need_mask);
-            // pass 1: row maximum
-            float mx = -INFINITY;
+            // The whole S row (128 fp32) is pulled into registers with one wait: TMEM load
+            // latency is paid once per tile instead of once per chunk.
 #pragma unroll
-            for (int cc = 0; cc < kBN / 32; ++cc) {
-                tc5::ld32(tS + cc * 32, v);
-                tc5::wait_ld();
-                if (warp_mask) {
+            for (int cc = 0; cc < kBN / 32; ++cc) tc5::ld32(tS + cc * 32, sv[cc]);
+            tc5::wait_ld();
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            if (warp_mask) {
+#pragma unroll
+                for (int cc = 0; cc < kBN / 32; ++cc)
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (key0 + cc * 32 + i <= lim) mx = fmaxf(mx, __uint_as_float(v[i]));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-                }
+                        if (key0 + cc * 32 + i > lim) sv[cc][i] = 0xff800000u;   // -inf
             }
+#pragma unroll
+            for (int cc = 0; cc < kBN / 32; ++cc)
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(sv[cc][i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(sv[cc][i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(sv[cc][i + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(sv[cc][i + 3]));
+                }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             const float m_new = fmaxf(m_ref, mx * c);
             const bool grow = m_new > m_ref + kRescaleThreshold;   // also true for the first finite max
             if (__any_sync(0xffffffffu, grow)) {
@@ -250,38 +258,36 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
                 if (j > 0) {
                     // S(j) complete implies PV(j-1) complete (one thread issues both, in order),
                     // so O_t is at rest until this group hands P(j) over.
-#pragma unroll
-                    for (int cc = 0; cc < kD / 32; ++cc) {
-                        tc5::ld32(tO + cc * 32, v);
+#pragma unroll 1
+                    for (int cc = 0; cc < kD / 16; ++cc) {
+                        uint32_t ov[16];
+                        tc5::ld16(tO + cc * 16, ov);
                         tc5::wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                        tc5::st32(tO + cc * 32, v);
+                        for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                        tc5::st16(tO + cc * 16, ov);
                     }
                 }
                 l *= corr;
                 if (grow) m_ref = m_new;
             }
             const float sub = m_ref == -INFINITY ? 0.f : m_ref;   // fully masked so far: stay finite
-            // pass 2: P = exp2(S*c - m), row sum, 16-bit P back into the S columns
+            // P = exp2(S*c - m) (masked entries are -inf -> 0), row sum, 16-bit P into the S columns
+            float l0 = 0.f, l1 = 0.f;
 #pragma unroll
             for (int cc = 0; cc < kBN / 32; ++cc) {
-                tc5::ld32(tS + cc * 32, v);
-                tc5::wait_ld();
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), c, -sub));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), c, -sub));
-                    if (warp_mask) {
-                        if (key0 + cc * 32 + i > lim) p0 = 0.f;
-                        if (key0 + cc * 32 + i + 1 > lim) p1 = 0.f;
-                    }
-                    l += p0 + p1;
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[cc][i]), c, -sub));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[cc][i + 1]), c, -sub));
+                    l0 += p0;
+                    l1 += p1;
                     pk[i >> 1] = pack2<T>(p0, p1);
                 }
                 tc5::st16(tS + cc * 16, pk);
             }
+            l += l0 + l1;
             tc5::wait_st();
             tc5::fence_before_sync();
             __syncwarp();
@@ -300,20 +306,20 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
             for (int cc = 0; cc < kD / 32; ++cc) {
                 if (ntiles > 0) {
-                    tc5::ld32(tO + cc * 32, v);
+                    tc5::ld32(tO + cc * 32, sv[0]);
                     tc5::wait_ld();
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = 0u;
+                    for (int i = 0; i < 32; ++i) sv[0][i] = 0u;
                 }
                 if (qi < len_q) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 w;
-                        w.x = pack2<T>(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-                        w.y = pack2<T>(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-                        w.z = pack2<T>(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-                        w.w = pack2<T>(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+                        w.x = pack2<T>(__uint_as_float(sv[0][i]) * inv, __uint_as_float(sv[0][i + 1]) * inv);
+                        w.y = pack2<T>(__uint_as_float(sv[0][i + 2]) * inv, __uint_as_float(sv[0][i + 3]) * inv);
+                        w.z = pack2<T>(__uint_as_float(sv[0][i + 4]) * inv, __uint_as_float(sv[0][i + 5]) * inv);
+                        w.w = pack2<T>(__uint_as_float(sv[0][i + 6]) * inv, __uint_as_float(sv[0][i + 7]) * inv);
                         *reinterpret_cast<uint4*>(orow + cc * 32 + i) = w;
                     }
                 }
