@@ -6,9 +6,12 @@ module raises, and so does every op of the package.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libb200mops.so"
+# B200MOPS_LIBRARY may point at another build of the same ABI (e.g. one compiled with tracing).
+LIB_PATH = Path(os.environ.get("B200MOPS_LIBRARY") or
+                Path(__file__).resolve().parent / "lib" / "libb200mops.so")
 
 BF16, F16, F32 = 0, 1, 2
 

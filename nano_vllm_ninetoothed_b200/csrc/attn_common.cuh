@@ -139,6 +139,21 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// 2^x on the FMA pipe (no MUFU): round-to-nearest split x = n + f, f in [-0.5, 0.5], a cubic
+// for 2^f (max relative error 1.6e-4) and n added straight into the exponent field.  Inputs
+// below -126 (including -inf) clamp to 2^-126.  Used to take load off the special-function
+// unit, which otherwise caps softmax throughput.
+__device__ __forceinline__ float poly_exp2(float x) {
+    x = fmaxf(x, -126.f);
+    const float magic = 12582912.f;          // 1.5 * 2^23: the integer part lands in the low mantissa bits
+    const float xr = x + magic;
+    const float f = x - (xr - magic);
+    float p = fmaf(f, 0.05360212f, 0.24237292f);
+    p = fmaf(p, f, 0.69350237f);
+    p = fmaf(p, f, 0.99994814f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
+}
+
 // ---------------------------------------------------------------- host: tensor maps
 // cuTensorMapEncodeTiled is fetched through the runtime so that the library does not link
 // against the driver stub.

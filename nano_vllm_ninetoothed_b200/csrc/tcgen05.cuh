@@ -23,6 +23,17 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
                  : "memory");
 }
 
+// True in exactly one (converged) lane of the calling warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ void fence_before_sync() {
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -126,6 +137,52 @@ __device__ __forceinline__ void st16(uint32_t addr, const uint32_t (&r)[16]) {
           "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
           "r"(r[14]), "r"(r[15])
         : "memory");
+}
+
+// ---------------------------------------------------------------- sm_100 scalar-pipe helpers
+// Three-input maximum and packed two-wide fp32 arithmetic (one issue slot for two lanes of
+// work), both new with sm_100; they roughly halve the FMA/ALU instruction count of softmax.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack_f32x2(float lo, float hi) {
+    f32x2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ void unpack_f32x2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+// 2^x for both halves on the FMA pipe; same scheme as poly_exp2 (cubic on [-0.5, 0.5]).
+__device__ __forceinline__ void poly_exp2_x2(f32x2 x, float& r0, float& r1) {
+    float x0, x1;
+    unpack_f32x2(x, x0, x1);
+    const f32x2 xc = pack_f32x2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+    const f32x2 magic = pack_f32x2(12582912.f, 12582912.f);
+    const f32x2 nmagic = pack_f32x2(-12582912.f, -12582912.f);
+    const f32x2 xr = add2(xc, magic);
+    const f32x2 f = fma2(add2(xr, nmagic), pack_f32x2(-1.f, -1.f), xc);
+    f32x2 p = fma2(f, pack_f32x2(0.05360212f, 0.05360212f), pack_f32x2(0.24237292f, 0.24237292f));
+    p = fma2(p, f, pack_f32x2(0.69350237f, 0.69350237f));
+    p = fma2(p, f, pack_f32x2(0.99994814f, 0.99994814f));
+    float p0, p1, n0, n1;
+    unpack_f32x2(p, p0, p1);
+    unpack_f32x2(xr, n0, n1);
+    r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(n0) << 23));
+    r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(n1) << 23));
 }
 
 }  // namespace tc5

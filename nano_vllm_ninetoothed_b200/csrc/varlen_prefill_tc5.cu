@@ -24,6 +24,7 @@
 // Every mbarrier wait is bounded; on a timeout the roles fall through to the common exit,
 // which frees the tensor memory.
 #include <math.h>
+#include <stdlib.h>
 
 #include <type_traits>
 
@@ -50,9 +51,22 @@ constexpr int kOffQ = 0;                                   // 2 tiles
 constexpr int kOffK = kOffQ + 2 * kTileBytes;              // kKVStages tiles
 constexpr int kOffV = kOffK + kKVStages * kTileBytes;
 constexpr int kOffBar = kOffV + kKVStages * kTileBytes;
-// barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_done
+// barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2],
+//           p_full[2], o_done
 constexpr int kNumBars = 1 + 4 * kKVStages + 2 + 2 + 1;
 constexpr int kSmemBytes = 1024 + kOffBar + kNumBars * 8 + 16;
+
+#ifdef B200MOPS_TC5_TRACE
+// Development aid (not compiled by default): CTA (0,0,0) stamps clock64 at phase boundaries.
+__device__ long long g_tc5_trace[3][32][8];
+#define TC5_TRACE(role, j, slot)                                                        \
+    do {                                                                                \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 32)          \
+            g_tc5_trace[role][j][slot] = clock64();                                     \
+    } while (0)
+#else
+#define TC5_TRACE(role, j, slot) do {} while (0)
+#endif
 
 struct Tc5Params {
     void* out; int64_t out_stride_t, out_stride_h;
@@ -62,7 +76,7 @@ struct Tc5Params {
     int32_t* status;
 };
 
-template <typename T>
+template <typename T, int kPolyMask>
 __global__ void __launch_bounds__(kThreads, 1)
 varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
                           const __grid_constant__ CUtensorMap tm_k,
@@ -147,66 +161,88 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
     } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0 && ntiles > 0) {
+        // The whole warp runs this loop so that descriptor arithmetic stays warp-uniform (it can
+        // live in uniform registers); one elected lane executes the tcgen05 instructions.  The
+        // issuing thread is the pacemaker of the tensor pipe: every cycle it spends between two
+        // tcgen05.mma is a cycle the pipe may idle, so nothing here is recomputed per MMA.
+        if (ntiles > 0) {
             constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
             constexpr uint32_t idesc_s = tc5::instr_desc_f16(fmt, kBM, kBN, 0, 0);
             constexpr uint32_t idesc_o = tc5::instr_desc_f16(fmt, kBM, kD, 0, 1);
-            bool ok = mbar_wait(bar(Q_FULL), 0, p.status);
+            const bool leader = tc5::elect_one();
+            const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+            const uint64_t dq = tc5::smem_desc_sw128(sbase + kOffQ, 16, 1024);
+            const uint64_t dk = tc5::smem_desc_sw128(sbase + kOffK, 16, 1024);
+            const uint64_t dv = tc5::smem_desc_sw128(sbase + kOffV, kHalf, 1024);
+            auto wait = [&](int b, uint32_t parity) {
+                const bool done = mbar_wait(bar(b), parity, p.status);
+                return __all_sync(0xffffffffu, done);
+            };
             // S_t = Q_t K_j^T : 8 k-steps of 16 over head_dim, both operands K-major
             auto issue_s = [&](int t, int j) {
-                const int s = j % kKVStages;
-                const uint32_t qa = sbase + kOffQ + t * kTileBytes;
-                const uint32_t kb = sbase + kOffK + s * kTileBytes;
+                const uint64_t a0 = dq + ((uint32_t)(t * kTileBytes) >> 4);
+                const uint64_t b0 = dk + ((uint32_t)((j % kKVStages) * kTileBytes) >> 4);
+                if (leader) {
 #pragma unroll
-                for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint32_t o = (ks >> 2) * kHalf + (ks & 3) * 32;
-                    tc5::mma_ss(tmem + t * kBN, tc5::smem_desc_sw128(qa + o, 16, 1024),
-                                tc5::smem_desc_sw128(kb + o, 16, 1024), idesc_s, ks > 0);
+                    for (int ks = 0; ks < kD / 16; ++ks) {
+                        const uint32_t o = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
+                        tc5::mma_ss(tm + t * kBN, a0 + o, b0 + o, idesc_s, ks > 0);
+                    }
+                    tc5::commit(bar(S_FULL + t));
                 }
-                tc5::commit(bar(S_FULL + t));
             };
             // O_t += P_t V_j : 8 k-steps of 16 keys; A = P from TMEM, B = V MN-major
             auto issue_pv = [&](int t, int j) {
-                const int s = j % kKVStages;
-                const uint32_t vb = sbase + kOffV + s * kTileBytes;
+                const uint64_t b0 = dv + ((uint32_t)((j % kKVStages) * kTileBytes) >> 4);
+                const uint32_t acc0 = j > 0 ? 1u : 0u;
+                if (leader) {
 #pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk) {
-                    tc5::mma_ts(tmem + 256 + t * kD, tmem + t * kBN + kk * 8,
-                                tc5::smem_desc_sw128(vb + kk * 2048, kHalf, 1024), idesc_o,
-                                (j > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < kBN / 16; ++kk)
+                        tc5::mma_ts(tm + 256 + t * kD, tm + t * kBN + kk * 8,
+                                    b0 + (uint32_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : acc0);
                 }
             };
-            if (ok) ok = mbar_wait(bar(K_FULL + 0), 0, p.status);
+            bool ok = wait(Q_FULL, 0) && wait(K_FULL + 0, 0);
             if (ok) {
                 tc5::fence_after_sync();
+                TC5_TRACE(2, 31, 0);
                 issue_s(0, 0);
+                TC5_TRACE(2, 31, 1);
                 issue_s(1, 0);
-                tc5::commit(bar(K_EMPTY + 0));
+                TC5_TRACE(2, 31, 2);
+                if (leader) tc5::commit(bar(K_EMPTY + 0));
             }
             for (int j = 0; ok && j < ntiles; ++j) {
                 const int s = j % kKVStages, sn = (j + 1) % kKVStages;
                 const uint32_t ph = (uint32_t)(j / kKVStages) & 1u;
                 const uint32_t phn = (uint32_t)((j + 1) / kKVStages) & 1u;
                 const bool more = j + 1 < ntiles;
-                if (!(ok = mbar_wait(bar(V_FULL + s), ph, p.status))) break;
-                if (!(ok = mbar_wait(bar(P_FULL + 0), (uint32_t)j & 1u, p.status))) break;
+                TC5_TRACE(2, j, 6);
+                if (!(ok = wait(V_FULL + s, ph))) break;
+                if (!(ok = wait(P_FULL + 0, (uint32_t)j & 1u))) break;
+                TC5_TRACE(2, j, 0);
                 tc5::fence_after_sync();
                 issue_pv(0, j);
+                TC5_TRACE(2, j, 1);
                 if (more) {
-                    if (!(ok = mbar_wait(bar(K_FULL + sn), phn, p.status))) break;
+                    if (!(ok = wait(K_FULL + sn, phn))) break;
                     tc5::fence_after_sync();
                     issue_s(0, j + 1);
                 }
-                if (!(ok = mbar_wait(bar(P_FULL + 1), (uint32_t)j & 1u, p.status))) break;
+                TC5_TRACE(2, j, 2);
+                if (!(ok = wait(P_FULL + 1, (uint32_t)j & 1u))) break;
+                TC5_TRACE(2, j, 3);
                 tc5::fence_after_sync();
                 issue_pv(1, j);
-                tc5::commit(bar(V_EMPTY + s));
+                if (leader) tc5::commit(bar(V_EMPTY + s));
+                TC5_TRACE(2, j, 4);
                 if (more) {
                     issue_s(1, j + 1);
-                    tc5::commit(bar(K_EMPTY + sn));
+                    if (leader) tc5::commit(bar(K_EMPTY + sn));
                 }
+                TC5_TRACE(2, j, 5);
             }
-            tc5::commit(bar(O_DONE));
+            if (leader) tc5::commit(bar(O_DONE));
         }
     } else {
         // ------------------------------------------------------------ softmax groups
@@ -224,6 +260,7 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (int j = 0; j < ntiles; ++j) {
             ok = mbar_wait(bar(S_FULL + t), (uint32_t)j & 1u, p.status);
             if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+            if (threadIdx.x % 128 == 0) TC5_TRACE(t, j, 0);
             tc5::fence_after_sync();
             const int key0 = j * kBN;
             const bool need_mask = key0 + kBN - 1 > lim;      // this row crosses its limit here
@@ -233,6 +270,7 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
             for (int cc = 0; cc < kBN / 32; ++cc) tc5::ld32(tS + cc * 32, sv[cc]);
             tc5::wait_ld();
+            if (threadIdx.x % 128 == 0) TC5_TRACE(t, j, 1);
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
             if (warp_mask) {
 #pragma unroll
@@ -244,11 +282,11 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
             for (int cc = 0; cc < kBN / 32; ++cc)
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    mx0 = fmaxf(mx0, __uint_as_float(sv[cc][i]));
-                    mx1 = fmaxf(mx1, __uint_as_float(sv[cc][i + 1]));
-                    mx2 = fmaxf(mx2, __uint_as_float(sv[cc][i + 2]));
-                    mx3 = fmaxf(mx3, __uint_as_float(sv[cc][i + 3]));
+                for (int i = 0; i < 32; i += 8) {
+                    mx0 = tc5::max3(mx0, __uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1]));
+                    mx1 = tc5::max3(mx1, __uint_as_float(sv[cc][i + 2]), __uint_as_float(sv[cc][i + 3]));
+                    mx2 = tc5::max3(mx2, __uint_as_float(sv[cc][i + 4]), __uint_as_float(sv[cc][i + 5]));
+                    mx3 = tc5::max3(mx3, __uint_as_float(sv[cc][i + 6]), __uint_as_float(sv[cc][i + 7]));
                 }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             const float m_new = fmaxf(m_ref, mx * c);
@@ -272,26 +310,52 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
                 if (grow) m_ref = m_new;
             }
             const float sub = m_ref == -INFINITY ? 0.f : m_ref;   // fully masked so far: stay finite
+            if (threadIdx.x % 128 == 0) TC5_TRACE(t, j, 2);
             // P = exp2(S*c - m) (masked entries are -inf -> 0), row sum, 16-bit P into the S columns
-            float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-            for (int cc = 0; cc < kBN / 32; ++cc) {
+            // Packed fp32x2 arithmetic for the scale/subtract and the row sum; in tiles that need
+            // no mask three pairs in eight take the polynomial exp2 on the FMA pipe, which
+            // balances it against the special-function unit (masked entries must come out as
+            // exact zeros, which only ex2 gives, so masked tiles use ex2 throughout).
+            const tc5::f32x2 c2 = tc5::pack_f32x2(c, c), nsub2 = tc5::pack_f32x2(-sub, -sub);
+            tc5::f32x2 lsum = tc5::pack_f32x2(0.f, 0.f);
+            auto p_chunk = [&](int cc, auto use_poly) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[cc][i]), c, -sub));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[cc][i + 1]), c, -sub));
-                    l0 += p0;
-                    l1 += p1;
+                    const tc5::f32x2 x = tc5::fma2(
+                        tc5::pack_f32x2(__uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1])), c2, nsub2);
+                    float p0, p1;
+                    const int k8 = (i >> 1) & 7;
+                    if (decltype(use_poly)::value && ((kPolyMask >> k8) & 1)) {
+                        tc5::poly_exp2_x2(x, p0, p1);
+                    } else {
+                        float x0, x1;
+                        tc5::unpack_f32x2(x, x0, x1);
+                        p0 = fast_exp2(x0);
+                        p1 = fast_exp2(x1);
+                    }
+                    lsum = tc5::add2(lsum, tc5::pack_f32x2(p0, p1));
                     pk[i >> 1] = pack2<T>(p0, p1);
                 }
                 tc5::st16(tS + cc * 16, pk);
+            };
+            if (warp_mask) {
+#pragma unroll
+                for (int cc = 0; cc < kBN / 32; ++cc) p_chunk(cc, std::false_type{});
+            } else {
+#pragma unroll
+                for (int cc = 0; cc < kBN / 32; ++cc) p_chunk(cc, std::true_type{});
             }
-            l += l0 + l1;
             tc5::wait_st();
             tc5::fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(P_FULL + t));
+            if (threadIdx.x % 128 == 0) TC5_TRACE(t, j, 3);
+            {
+                float l0, l1;
+                tc5::unpack_f32x2(lsum, l0, l1);
+                l += l0 + l1;
+            }
         }
         // ------------------------------------------------------------ epilogue
         if (ok && ntiles > 0) {
@@ -339,6 +403,12 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
 
 }  // namespace
 
+#ifdef B200MOPS_TC5_TRACE
+extern "C" int b200mops_debug_tc5_trace(long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_tc5_trace, sizeof(g_tc5_trace)) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 int launch_varlen_prefill_tc5(const b200mops_varlen_prefill_args* a, const CUtensorMap& tm_q,
                               const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st) {
     Tc5Params p;
@@ -350,17 +420,33 @@ int launch_varlen_prefill_tc5(const b200mops_varlen_prefill_args* a, const CUten
     p.status = a->status_word;
     const dim3 grid((unsigned)((a->max_seqlen_q + kBM - 1) / kBM), (unsigned)(a->hq / 2),
                     (unsigned)a->batch);
-    if (a->dtype == B200MOPS_BF16) {
-        if (cudaFuncSetAttribute(varlen_prefill_tc5_kernel<__nv_bfloat16>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+    // Pairs (of every eight) whose exp2 runs as a polynomial on the FMA pipe instead of on the
+    // special-function unit.  B200MOPS_TC5_POLY (0..4) overrides the default for measurements.
+    static const int poly_pairs = [] {
+        const char* e = getenv("B200MOPS_TC5_POLY");
+        return e ? atoi(e) : 3;
+    }();
+    auto launch = [&](auto kernel) -> int {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+            cudaSuccess)
             return B200MOPS_ERR_LAUNCH;
-        varlen_prefill_tc5_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, st>>>(tm_q, tm_k, tm_v, p);
-    } else {
-        if (cudaFuncSetAttribute(varlen_prefill_tc5_kernel<__half>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-            return B200MOPS_ERR_LAUNCH;
-        varlen_prefill_tc5_kernel<__half><<<grid, kThreads, kSmemBytes, st>>>(tm_q, tm_k, tm_v, p);
+        kernel<<<grid, kThreads, kSmemBytes, st>>>(tm_q, tm_k, tm_v, p);
+        return launch_status();
+    };
+#define B200MOPS_TC5_DISPATCH(TYPE)                                                    \
+    switch (poly_pairs) {                                                              \
+        case 0: return launch(varlen_prefill_tc5_kernel<TYPE, 0x00>);                  \
+        case 1: return launch(varlen_prefill_tc5_kernel<TYPE, 0x10>);                  \
+        case 2: return launch(varlen_prefill_tc5_kernel<TYPE, 0x22>);                  \
+        case 4: return launch(varlen_prefill_tc5_kernel<TYPE, 0xAA>);                  \
+        default: return launch(varlen_prefill_tc5_kernel<TYPE, 0x52>);                 \
     }
+    if (a->dtype == B200MOPS_BF16) {
+        B200MOPS_TC5_DISPATCH(__nv_bfloat16)
+    } else {
+        B200MOPS_TC5_DISPATCH(__half)
+    }
+#undef B200MOPS_TC5_DISPATCH
     return launch_status();
 }
 
