@@ -188,6 +188,9 @@ def graph_of(fn_list):
 def cpu_baseline_decode(lens: list[int], budget_s: float = 12.0) -> dict:
     """The oracle's paged decode on the host cores over the first sequences of the workload."""
     from oracle import mops_oracle as O
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core it can.
+    torch.set_num_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity")
+                          else (os.cpu_count() or 1))
     n_seq = 24
     sample = lens[:n_seq]
     case = W.make_decode_case(seed=0, lens=sample, hq=HQ, hkv=HKV, page=PAGE)

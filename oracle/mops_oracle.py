@@ -13,14 +13,16 @@ How the parity of this restatement is pinned:
   UNMODIFIED from the reference tree, runs it on seeded inputs and commits inputs' seeds and
   outputs under `tests/golden/`; `tests/test_oracle_golden.py` requires this restatement to
   reproduce those outputs bit for bit.
-* `store_kvcache` and the two attention operators have no CPU implementation in the reference
-  (they forward to a Triton kernel and to the un-vendored `flash-attn` wheel,
-  mops/torch/ops.py:62-76).  They are restated from the reference's own statement of their
-  semantics (cited per function).  For attention, `tests/golden/make_golden_flash_attn.py`
-  additionally records the outputs of `flash_attn` itself -- the very calls the reference's
-  torch backend forwards to -- on a B200; when those fixtures are present the restatement is
-  checked against them within the bf16 tolerance.  Where they are absent, attention parity is
-  "unpinned" beyond the reference's commented pure-torch decode (mops/torch/ops.py:78-125).
+* The two attention operators have no CPU implementation in the reference: its torch backend
+  forwards them to the un-vendored `flash-attn` wheel (mops/torch/ops.py:68-76).  They are
+  restated from the reference's own statements of their semantics (cited per function), and
+  `tests/golden/make_golden_flash_attn.py` records the outputs of `flash_attn` itself -- the
+  very calls the reference makes -- on a B200 (`tests/golden/flash_attn_outputs.pt`);
+  `tests/test_oracle_golden.py` requires this restatement to match them within the 16-bit
+  tolerance (2e-2 abs / 1e-2 rel).
+* `store_kvcache` forwards to a Triton kernel (mops/torch/ops.py:62-65) that cannot run
+  without a GPU and has no fixtures: restated from mops/triton/attention.py:7-38, parity
+  unpinned beyond that statement.
 
 Every function takes and returns CPU tensors and follows the reference's order of arithmetic
 and rounding.

@@ -259,3 +259,24 @@ def test_prefill_full_size_heads_sample_against_oracle(mops, oracle):
                                              p.v[:, hk:hk + 1].cpu(), cu, cu, p.max_seqlen,
                                              p.max_seqlen, softmax_scale=p.softmax_scale, causal=True)
         close(out[:, hq_i:hq_i + 1], want)
+
+
+# ------------------------------------------------------------------ flash-attn recorded outputs
+def test_kernels_match_recorded_flash_attn_outputs(mops):
+    """Same seeded cases whose outputs were recorded from flash-attn (the library the reference's
+    torch backend forwards to) on a B200."""
+    from tests.test_oracle_golden import FA_CASES, FA_MOD, FA_RECORD
+    for name, case in FA_CASES.items():
+        if FA_MOD.case_digests(case) != FA_RECORD["input_digests"][name]:
+            pytest.skip("torch's CPU random stream differs from the fixture's")
+        d = case.to(DEV)
+        if isinstance(case, W.DecodeCase):
+            got = mops.flash_attn_with_kvcache(d.q, d.k_cache, d.v_cache, cache_seqlens=d.cache_seqlens,
+                                               block_table=d.block_table,
+                                               softmax_scale=d.softmax_scale, causal=True)
+        else:
+            got = mops.flash_attn_varlen_func(d.q, d.k, d.v, max_seqlen_q=d.max_seqlen,
+                                              cu_seqlens_q=d.cu_seqlens, max_seqlen_k=d.max_seqlen,
+                                              cu_seqlens_k=d.cu_seqlens,
+                                              softmax_scale=d.softmax_scale, causal=True)
+        close(got, FA_RECORD["outputs"][name])

@@ -126,3 +126,38 @@ def test_store_kvcache_oracle_skips_minus_one_and_is_exact():
         assert torch.equal(flat_k[s], key[i].reshape(-1))
         assert torch.equal(flat_v[s], value[i].reshape(-1))
     assert not flat_k[~written].any() and not flat_v[~written].any()
+
+
+# ---------------------------------------------------------------- flash-attn recorded outputs
+def _load_flash_golden():
+    spec = importlib.util.spec_from_file_location("make_golden_flash_attn",
+                                                  GOLDEN_DIR / "make_golden_flash_attn.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod, torch.load(GOLDEN_DIR / "flash_attn_outputs.pt")
+
+
+FA_MOD, FA_RECORD = _load_flash_golden()
+FA_CASES = FA_MOD.attention_cases()
+
+
+@pytest.mark.parametrize("name", sorted(FA_RECORD["outputs"]))
+def test_attention_oracle_matches_recorded_flash_attn(name):
+    """The reference's torch backend forwards attention to flash-attn unchanged; these outputs
+    were recorded from flash-attn 2.8.3 on a B200 with the reference's own call patterns."""
+    from nano_vllm_ninetoothed_b200 import workloads as W
+    case = FA_CASES[name]
+    if FA_MOD.case_digests(case) != FA_RECORD["input_digests"][name]:
+        pytest.skip("torch's CPU random stream differs from the one the fixture was made with")
+    if isinstance(case, W.DecodeCase):
+        got = O.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                        cache_seqlens=case.cache_seqlens,
+                                        block_table=case.block_table,
+                                        softmax_scale=case.softmax_scale, causal=True)
+    else:
+        got = O.flash_attn_varlen_func(case.q, case.k, case.v, case.cu_seqlens, case.cu_seqlens,
+                                       case.max_seqlen, case.max_seqlen,
+                                       softmax_scale=case.softmax_scale, causal=True)
+    want = FA_RECORD["outputs"][name]
+    assert got.shape == want.shape and got.dtype == want.dtype
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=1e-2)
