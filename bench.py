@@ -295,7 +295,35 @@ def bench_side_ops(mops, dev, rank: int, world: int, steps: int, warmup: int, pk
     gbs = W.embedding_bytes(t, 1024) / (ms * 1e-3) / 1e9
     out["embedding"] = {"ids": t, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"],
                         "note": "311 MB table, random rows; six id sets"}
-    out["timing"] = "CUDA-graph replay of six calls on six input sets, events around the replays"
+    del table, id_sets
+    # the remaining per-layer operators at Qwen3-0.6B prefill shapes (T tokens)
+    g = torch.Generator().manual_seed(5)
+    qkv_sets = [torch.randn(t, (16 + 2 * 8) * 128, generator=g).bfloat16().to(dev) for _ in range(n_sets)]
+    w128 = (1 + 0.02 * torch.randn(128, generator=g)).bfloat16().to(dev)
+    ms = per_call_ms([(lambda x=x: mops.rms_forward(x[:, :2048].view(t, 16, 128), w128, 1e-6)) for x in qkv_sets])
+    gbs = (t * 16 * 128 * 2 * 2) / (ms * 1e-3) / 1e9
+    out["rms_forward_qnorm"] = {"rows": t * 16, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"],
+                                "note": "strided [T,16,128] view of the qkv activation, read + write"}
+    cache = torch.randn(4096, 1, 128, generator=g).to(dev)
+    pos = torch.randint(0, 4096, (t,), generator=g).to(dev)
+    cos, sin = cache[pos].chunk(2, dim=-1)
+    q_sets = [x[:, :2048].reshape(t, 16, 128).contiguous() for x in qkv_sets]
+    ms = per_call_ms([(lambda q=q: mops.apply_rotary_emb(q, cos, sin)) for q in q_sets])
+    gbs = (t * 16 * 128 * 2 * 2 + t * 128 * 4) / (ms * 1e-3) / 1e9
+    out["apply_rotary_emb"] = {"rows": t * 16, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
+    del qkv_sets, q_sets
+    gu_sets = [torch.randn(t, 2 * 3072, generator=g).bfloat16().to(dev) for _ in range(n_sets)]
+    ms = per_call_ms([(lambda x=x: mops.siluAndMul(*x.chunk(2, -1))) for x in gu_sets])
+    gbs = (t * 3072 * 2 * 3) / (ms * 1e-3) / 1e9
+    out["siluAndMul"] = {"rows": t, "gbs": gbs, "ms": ms, "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
+    del gu_sets
+    logit_sets = [torch.randn(256, 151936, generator=g).bfloat16().to(dev) for _ in range(3)]
+    temps = torch.full((256,), 0.6, device=dev)
+    ms = per_call_ms([(lambda x=x: mops.sampler_forward(x, temps)) for x in logit_sets])
+    gbs = (256 * 151936 * 2) / (ms * 1e-3) / 1e9
+    out["sampler_forward"] = {"rows": 256, "vocab": 151936, "gbs": gbs, "ms": ms,
+                              "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
+    out["timing"] = "CUDA-graph replay of the calls over rotating input sets, events around the replays"
     return out
 
 

@@ -321,7 +321,8 @@ extern "C" int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* a, vo
         const char* e = getenv("B200MOPS_PREFILL_KERNEL");
         return e != nullptr && strcmp(e, "mma") == 0;
     }();
-    const bool use_tc5 = !paged && ((a->hq / a->hkv) % 2 == 0) && !force_mma;
+    const bool use_tc5 = !paged && ((a->hq / a->hkv) % 2 == 0) && !force_mma &&
+                         a->batch <= kTc5MaxBatch && a->max_seqlen_q <= (int64_t)128 * kTc5MaxLevels;
     const uint32_t kv_box_rows = use_tc5 ? 128u : (uint32_t)kBN;
 
     CUtensorMap tm_q, tm_k, tm_v;

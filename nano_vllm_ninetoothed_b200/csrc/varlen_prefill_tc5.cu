@@ -1,13 +1,15 @@
 // Variable-length causal prefill attention on the Blackwell tensor cores (tcgen05 + TMEM).
 //
-// One CTA = one 128-row query tile of one sequence for TWO query heads that share a KV head
-// (G = hq/hkv must be even), so every K/V tile fetched serves two S tiles and the two tiles
-// keep the tensor pipe busy while the other one is in softmax.
+// Persistent kernel: one CTA per SM walks a static, heaviest-first list of work items.  A work
+// item is one 128-row query tile of one sequence for TWO query heads that share a KV head
+// (G = hq/hkv must be even), so every K/V tile fetched serves two S tiles, both tiles have the
+// same causal extent, and one tile's MMAs run while the other tile is in softmax.
 //
 //   warps 0-3  softmax group 0 (query head 2p)     one thread per query row == TMEM lane
 //   warps 4-7  softmax group 1 (query head 2p+1)
-//   warp  8    MMA issuer: a single thread issues every tcgen05.mma and tcgen05.commit
-//   warp  9    TMA producer: Q tiles once, then 128-key K and V tiles through 2-stage rings
+//   warp  8    MMA issuer: the warp runs the loop uniformly, one elected lane issues every
+//              tcgen05.mma / tcgen05.commit
+//   warp  9    TMA producer: Q tiles per item, 128-key K and V tiles through 2-stage rings
 //
 //   TMEM (512 columns x 128 lanes, fp32):  S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512)
 //   P (16-bit) overwrites the first 64 columns of its S tile and is read by the PV MMA
@@ -17,6 +19,14 @@
 //   per KV tile j:   S_t = Q_t K_j^T  ->  softmax group t: row max, lazy rescale of O_t,
 //                    P_t = exp2(S_t*c - m)  ->  O_t += P_t V_j
 //   issue order:     S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) | ...
+//
+// Schedule: items are ordered by row-tile index descending (a later row tile has more KV tiles
+// under the causal mask), sequences sorted by length inside a level, head pairs innermost, and
+// dealt round-robin to the CTAs, so every CTA gets one item of each weight class per round.
+// Every role derives the same item sequence from tables built once in shared memory.  All
+// pipeline state (ring stages, barrier phases) runs on across items: the producer prefetches
+// the next item's tiles, the MMA warp issues the next item's first S tiles right behind the
+// last PV, and a softmax group's epilogue (O from TMEM to global memory) overlaps them.
 //
 // Softmax state is per thread (a thread owns a whole row), so there are no shuffles.  The
 // running maximum is only raised when it grows by more than 2^8 (O and l stay consistent
@@ -40,7 +50,6 @@ constexpr int kD = 128;                  // head dim
 constexpr int kHalf = 128 * 128;         // bytes of one [128 x 64] 16-bit swizzled tile
 constexpr int kTileBytes = 2 * kHalf;    // a [128 x 128] operand = two halves
 constexpr int kKVStages = 2;
-constexpr int kSoftmaxThreads = 256;
 constexpr int kMmaWarp = 8, kLoadWarp = 9;
 constexpr int kThreads = 320;
 constexpr uint32_t kTmemCols = 512;
@@ -51,29 +60,44 @@ constexpr int kOffQ = 0;                                   // 2 tiles
 constexpr int kOffK = kOffQ + 2 * kTileBytes;              // kKVStages tiles
 constexpr int kOffV = kOffK + kKVStages * kTileBytes;
 constexpr int kOffBar = kOffV + kKVStages * kTileBytes;
-// barriers: q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2],
-//           p_full[2], o_done
-constexpr int kNumBars = 1 + 4 * kKVStages + 2 + 2 + 1;
-constexpr int kSmemBytes = 1024 + kOffBar + kNumBars * 8 + 16;
+// barriers: q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2],
+//           o_done[2], o_free[2]
+constexpr int kNumBars = 2 + 4 * kKVStages + 2 + 2 + 2 + 2;
+constexpr int kOffSched = kOffBar + kNumBars * 8 + 16;     // schedule tables (uint16)
+constexpr int kSchedBytes = (2 * kTc5MaxBatch + kTc5MaxLevels) * 2;
+constexpr int kSmemBytes = 1024 + kOffSched + kSchedBytes;
 
 #ifdef B200MOPS_TC5_TRACE
-// Development aid (not compiled by default): CTA (0,0,0) stamps clock64 at phase boundaries.
-__device__ long long g_tc5_trace[3][32][8];
-#define TC5_TRACE(role, j, slot)                                                        \
-    do {                                                                                \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 32)          \
-            g_tc5_trace[role][j][slot] = clock64();                                     \
+// Development aid (not compiled by default): per-CTA cycle accounting of the MMA warp.
+// [cta][0] total cycles, [1] tiles, [2..7] cycles waiting on V, O_FREE, P0, Q+K, P1, items.
+__device__ long long g_tc5_acct[256][8];
+#define TC5_ACCT(slot, expr)                                             \
+    do {                                                                 \
+        const long long t_ = clock64();                                  \
+        expr;                                                            \
+        if (blockIdx.x < 256) acct[slot] += clock64() - t_;              \
     } while (0)
 #else
-#define TC5_TRACE(role, j, slot) do {} while (0)
+#define TC5_ACCT(slot, expr) do { expr; } while (0)
 #endif
 
 struct Tc5Params {
     void* out; int64_t out_stride_t, out_stride_h;
     const int32_t* cu_q; const int32_t* cu_k;
-    int group, causal;
+    int batch, pairs, levels, group, causal;
     float scale_log2;
     int32_t* status;
+};
+
+// One work item, as every role decodes it.
+struct Item {
+    int hq0, hk, q_begin, len_q, k_begin, len_k, m0, off, ntiles;
+};
+
+// Position in the static schedule: `level` = row-tile index, `pos` = index inside the level
+// (sequence rank * pairs + pair).  Each CTA starts at its block index and strides by the grid.
+struct Cursor {
+    int level, pos;
 };
 
 template <typename T, int kPolyMask>
@@ -87,31 +111,29 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t sbase = smem_u32(smem);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    uint16_t* sched_mt = reinterpret_cast<uint16_t*>(smem + kOffSched);      // row tiles per sequence
+    uint16_t* sched_order = sched_mt + kTc5MaxBatch;                         // sequences, longest first
+    uint16_t* sched_cnt = sched_order + kTc5MaxBatch;                        // sequences with > level tiles
     const uint32_t bar0 = smem_u32(bars);
     auto bar = [&](int i) { return bar0 + 8u * i; };
-    constexpr int Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + kKVStages, V_FULL = K_EMPTY + kKVStages,
-                  V_EMPTY = V_FULL + kKVStages, S_FULL = V_EMPTY + kKVStages, P_FULL = S_FULL + 2,
-                  O_DONE = P_FULL + 2;
+    constexpr int Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = K_FULL + kKVStages,
+                  V_FULL = K_EMPTY + kKVStages, V_EMPTY = V_FULL + kKVStages,
+                  S_FULL = V_EMPTY + kKVStages, P_FULL = S_FULL + 2, O_DONE = P_FULL + 2,
+                  O_FREE = O_DONE + 2;
 
-    const int pair = blockIdx.y, b = blockIdx.z;
-    const int hq0 = pair * 2;
-    const int hk = hq0 / p.group;
-    const int q_begin = __ldg(p.cu_q + b), len_q = __ldg(p.cu_q + b + 1) - q_begin;
-    const int k_begin = __ldg(p.cu_k + b), len_k = __ldg(p.cu_k + b + 1) - k_begin;
-    const int m_tiles = (len_q + kBM - 1) / kBM;
-    if ((int)blockIdx.x >= m_tiles) return;
-    // Once any CTA of this stream of work has given up on a wait, the rest leave at once
-    // instead of each spending its own time limit.
+    // Once any CTA has given up on a wait, the rest leave at once instead of each spending
+    // its own time limit.
     if (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & B200MOPS_DEV_WAIT_TIMEOUT)) return;
-    const int m0 = (m_tiles - 1 - (int)blockIdx.x) * kBM;     // heavy (late) row tiles first
-    const int off = len_k - len_q;
-    int n_end = len_k;
-    if (p.causal) n_end = min(len_k, m0 + kBM + off);
-    const int ntiles = n_end > 0 ? (n_end + kBN - 1) / kBN : 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // ---------------------------------------------------------------- schedule tables
+    for (int b = threadIdx.x; b < p.batch; b += kThreads) {
+        const int lq = __ldg(p.cu_q + b + 1) - __ldg(p.cu_q + b);
+        sched_mt[b] = (uint16_t)min(p.levels, max(0, (lq + kBM - 1) / kBM));
+    }
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
+        mbar_init(bar(Q_EMPTY), 1);
         for (int s = 0; s < kKVStages; ++s) {
             mbar_init(bar(K_FULL + s), 1);
             mbar_init(bar(K_EMPTY + s), 1);
@@ -121,42 +143,99 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar(S_FULL + t), 1);
             mbar_init(bar(P_FULL + t), 4);      // one arrival per softmax warp
+            mbar_init(bar(O_FREE + t), 4);
+            mbar_init(bar(O_DONE + t), 1);
         }
-        mbar_init(bar(O_DONE), 1);
         mbar_fence_init();
     }
     if (warp == kMmaWarp) {
         tc5::tmem_alloc(smem_u32(tmem_slot), kTmemCols);
         tc5::tmem_relinquish();
     }
+    __syncthreads();
+    for (int b = threadIdx.x; b < p.batch; b += kThreads) {
+        const int mine = sched_mt[b];
+        int rank = 0;
+        for (int o = 0; o < p.batch; ++o) {
+            const int other = sched_mt[o];
+            rank += (other > mine) || (other == mine && o < b);
+        }
+        sched_order[rank] = (uint16_t)b;
+    }
+    for (int lv = threadIdx.x; lv < p.levels; lv += kThreads) {
+        int n = 0;
+        for (int o = 0; o < p.batch; ++o) n += sched_mt[o] > lv;
+        sched_cnt[lv] = (uint16_t)n;
+    }
     tc5::fence_before_sync();
     __syncthreads();
     tc5::fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
+    auto settle = [&](Cursor& cur) {          // skip exhausted levels
+        while (cur.level >= 0 && cur.pos >= (int)sched_cnt[cur.level] * p.pairs) {
+            cur.pos -= (int)sched_cnt[cur.level] * p.pairs;
+            --cur.level;
+        }
+    };
+    auto first_item = [&]() {
+        Cursor cur{p.levels - 1, (int)blockIdx.x};
+        settle(cur);
+        return cur;
+    };
+    auto next_item = [&](Cursor& cur) {
+        cur.pos += (int)gridDim.x;
+        settle(cur);
+    };
+    auto decode = [&](const Cursor& cur) {
+        Item it;
+        const int b = sched_order[cur.pos / p.pairs];
+        it.hq0 = (cur.pos % p.pairs) * 2;
+        it.hk = it.hq0 / p.group;
+        it.q_begin = __ldg(p.cu_q + b);
+        it.len_q = __ldg(p.cu_q + b + 1) - it.q_begin;
+        it.k_begin = __ldg(p.cu_k + b);
+        it.len_k = __ldg(p.cu_k + b + 1) - it.k_begin;
+        it.m0 = cur.level * kBM;
+        it.off = it.len_k - it.len_q;
+        int n_end = it.len_k;
+        if (p.causal) n_end = min(it.len_k, it.m0 + kBM + it.off);
+        it.ntiles = n_end > 0 ? (n_end + kBN - 1) / kBN : 0;
+        return it;
+    };
+
     if (warp == kLoadWarp) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0 && ntiles > 0) {
+        if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
-            mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
-            for (int t = 0; t < 2; ++t) {
-                const uint32_t dst = sbase + kOffQ + t * kTileBytes;
-                tma_load_4d(dst, &tm_q, bar(Q_FULL), 0, hq0 + t, q_begin + m0, 0);
-                tma_load_4d(dst + kHalf, &tm_q, bar(Q_FULL), 64, hq0 + t, q_begin + m0, 0);
-            }
-            for (int j = 0; j < ntiles; ++j) {
-                const int s = j % kKVStages, round = j / kKVStages;
-                const int row = k_begin + j * kBN;
-                if (round > 0 && !mbar_wait(bar(K_EMPTY + s), (uint32_t)(round - 1) & 1u, p.status)) break;
-                mbar_arrive_expect_tx(bar(K_FULL + s), kTileBytes);
-                tma_load_4d(sbase + kOffK + s * kTileBytes, &tm_k, bar(K_FULL + s), 0, hk, row, 0);
-                tma_load_4d(sbase + kOffK + s * kTileBytes + kHalf, &tm_k, bar(K_FULL + s), 64, hk, row, 0);
-                if (round > 0 && !mbar_wait(bar(V_EMPTY + s), (uint32_t)(round - 1) & 1u, p.status)) break;
-                mbar_arrive_expect_tx(bar(V_FULL + s), kTileBytes);
-                tma_load_4d(sbase + kOffV + s * kTileBytes, &tm_v, bar(V_FULL + s), 0, hk, row, 0);
-                tma_load_4d(sbase + kOffV + s * kTileBytes + kHalf, &tm_v, bar(V_FULL + s), 64, hk, row, 0);
+            int g = 0, n_act = 0;       // KV tiles and non-empty items handled so far
+            bool ok = true;
+            for (Cursor cur = first_item(); ok && cur.level >= 0; next_item(cur)) {
+                const Item it = decode(cur);
+                if (it.ntiles == 0) continue;
+                // the previous item's last S MMA has read the Q tiles
+                if (n_act > 0 && !(ok = mbar_wait(bar(Q_EMPTY), (uint32_t)(n_act - 1) & 1u, p.status))) break;
+                mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
+                for (int t = 0; t < 2; ++t) {
+                    const uint32_t dst = sbase + kOffQ + t * kTileBytes;
+                    tma_load_4d(dst, &tm_q, bar(Q_FULL), 0, it.hq0 + t, it.q_begin + it.m0, 0);
+                    tma_load_4d(dst + kHalf, &tm_q, bar(Q_FULL), 64, it.hq0 + t, it.q_begin + it.m0, 0);
+                }
+                for (int j = 0; j < it.ntiles; ++j, ++g) {
+                    const int s = g % kKVStages, round = g / kKVStages;
+                    const int row = it.k_begin + j * kBN;
+                    if (round > 0 && !(ok = mbar_wait(bar(K_EMPTY + s), (uint32_t)(round - 1) & 1u, p.status))) break;
+                    mbar_arrive_expect_tx(bar(K_FULL + s), kTileBytes);
+                    tma_load_4d(sbase + kOffK + s * kTileBytes, &tm_k, bar(K_FULL + s), 0, it.hk, row, 0);
+                    tma_load_4d(sbase + kOffK + s * kTileBytes + kHalf, &tm_k, bar(K_FULL + s), 64, it.hk, row, 0);
+                    if (round > 0 && !(ok = mbar_wait(bar(V_EMPTY + s), (uint32_t)(round - 1) & 1u, p.status))) break;
+                    mbar_arrive_expect_tx(bar(V_FULL + s), kTileBytes);
+                    tma_load_4d(sbase + kOffV + s * kTileBytes, &tm_v, bar(V_FULL + s), 0, it.hk, row, 0);
+                    tma_load_4d(sbase + kOffV + s * kTileBytes + kHalf, &tm_v, bar(V_FULL + s), 64, it.hk, row, 0);
+                }
+                ++n_act;
             }
         }
     } else if (warp == kMmaWarp) {
@@ -165,85 +244,139 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
         // live in uniform registers); one elected lane executes the tcgen05 instructions.  The
         // issuing thread is the pacemaker of the tensor pipe: every cycle it spends between two
         // tcgen05.mma is a cycle the pipe may idle, so nothing here is recomputed per MMA.
-        if (ntiles > 0) {
-            constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-            constexpr uint32_t idesc_s = tc5::instr_desc_f16(fmt, kBM, kBN, 0, 0);
-            constexpr uint32_t idesc_o = tc5::instr_desc_f16(fmt, kBM, kD, 0, 1);
-            const bool leader = tc5::elect_one();
-            const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
-            const uint64_t dq = tc5::smem_desc_sw128(sbase + kOffQ, 16, 1024);
-            const uint64_t dk = tc5::smem_desc_sw128(sbase + kOffK, 16, 1024);
-            const uint64_t dv = tc5::smem_desc_sw128(sbase + kOffV, kHalf, 1024);
-            auto wait = [&](int b, uint32_t parity) {
-                const bool done = mbar_wait(bar(b), parity, p.status);
-                return __all_sync(0xffffffffu, done);
-            };
-            // S_t = Q_t K_j^T : 8 k-steps of 16 over head_dim, both operands K-major
-            auto issue_s = [&](int t, int j) {
-                const uint64_t a0 = dq + ((uint32_t)(t * kTileBytes) >> 4);
-                const uint64_t b0 = dk + ((uint32_t)((j % kKVStages) * kTileBytes) >> 4);
-                if (leader) {
+        constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+        constexpr uint32_t idesc_s = tc5::instr_desc_f16(fmt, kBM, kBN, 0, 0);
+        constexpr uint32_t idesc_o = tc5::instr_desc_f16(fmt, kBM, kD, 0, 1);
+        const bool leader = tc5::elect_one();
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        const uint64_t dq = tc5::smem_desc_sw128(sbase + kOffQ, 16, 1024);
+        const uint64_t dk = tc5::smem_desc_sw128(sbase + kOffK, 16, 1024);
+        const uint64_t dv = tc5::smem_desc_sw128(sbase + kOffV, kHalf, 1024);
+        auto wait = [&](int b, uint32_t parity) {
+            const bool done = mbar_wait(bar(b), parity & 1u, p.status);
+            return __all_sync(0xffffffffu, done);
+        };
+        // S_t = Q_t K^T for ring tile g: 8 k-steps of 16 over head_dim, both operands K-major
+        auto issue_s = [&](int t, int g) {
+            const uint64_t a0 = dq + ((uint32_t)(t * kTileBytes) >> 4);
+            const uint64_t b0 = dk + ((uint32_t)((g % kKVStages) * kTileBytes) >> 4);
+            if (leader) {
 #pragma unroll
-                    for (int ks = 0; ks < kD / 16; ++ks) {
-                        const uint32_t o = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
-                        tc5::mma_ss(tm + t * kBN, a0 + o, b0 + o, idesc_s, ks > 0);
-                    }
-                    tc5::commit(bar(S_FULL + t));
+                for (int ks = 0; ks < kD / 16; ++ks) {
+                    const uint32_t o = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
+                    tc5::mma_ss(tm + t * kBN, a0 + o, b0 + o, idesc_s, ks > 0);
                 }
-            };
-            // O_t += P_t V_j : 8 k-steps of 16 keys; A = P from TMEM, B = V MN-major
-            auto issue_pv = [&](int t, int j) {
-                const uint64_t b0 = dv + ((uint32_t)((j % kKVStages) * kTileBytes) >> 4);
-                const uint32_t acc0 = j > 0 ? 1u : 0u;
-                if (leader) {
+                tc5::commit(bar(S_FULL + t));
+            }
+        };
+        // O_t (+)= P_t V for ring tile g: 8 k-steps of 16 keys; A = P from TMEM, B = V MN-major
+        auto issue_pv = [&](int t, int g, uint32_t acc0) {
+            const uint64_t b0 = dv + ((uint32_t)((g % kKVStages) * kTileBytes) >> 4);
+            if (leader) {
 #pragma unroll
-                    for (int kk = 0; kk < kBN / 16; ++kk)
-                        tc5::mma_ts(tm + 256 + t * kD, tm + t * kBN + kk * 8,
-                                    b0 + (uint32_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : acc0);
-                }
-            };
-            bool ok = wait(Q_FULL, 0) && wait(K_FULL + 0, 0);
-            if (ok) {
-                tc5::fence_after_sync();
-                TC5_TRACE(2, 31, 0);
-                issue_s(0, 0);
-                TC5_TRACE(2, 31, 1);
-                issue_s(1, 0);
-                TC5_TRACE(2, 31, 2);
-                if (leader) tc5::commit(bar(K_EMPTY + 0));
+                for (int kk = 0; kk < kBN / 16; ++kk)
+                    tc5::mma_ts(tm + 256 + t * kD, tm + t * kBN + kk * 8,
+                                b0 + (uint32_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : acc0);
             }
-            for (int j = 0; ok && j < ntiles; ++j) {
-                const int s = j % kKVStages, sn = (j + 1) % kKVStages;
-                const uint32_t ph = (uint32_t)(j / kKVStages) & 1u;
-                const uint32_t phn = (uint32_t)((j + 1) / kKVStages) & 1u;
-                const bool more = j + 1 < ntiles;
-                TC5_TRACE(2, j, 6);
-                if (!(ok = wait(V_FULL + s, ph))) break;
-                if (!(ok = wait(P_FULL + 0, (uint32_t)j & 1u))) break;
-                TC5_TRACE(2, j, 0);
-                tc5::fence_after_sync();
-                issue_pv(0, j);
-                TC5_TRACE(2, j, 1);
-                if (more) {
-                    if (!(ok = wait(K_FULL + sn, phn))) break;
-                    tc5::fence_after_sync();
-                    issue_s(0, j + 1);
-                }
-                TC5_TRACE(2, j, 2);
-                if (!(ok = wait(P_FULL + 1, (uint32_t)j & 1u))) break;
-                TC5_TRACE(2, j, 3);
-                tc5::fence_after_sync();
-                issue_pv(1, j);
-                if (leader) tc5::commit(bar(V_EMPTY + s));
-                TC5_TRACE(2, j, 4);
-                if (more) {
-                    issue_s(1, j + 1);
-                    if (leader) tc5::commit(bar(K_EMPTY + sn));
-                }
-                TC5_TRACE(2, j, 5);
+        };
+        // The KV tiles of all items form one stream: the tile after an item's last tile is the
+        // first tile of the next item, so the next item's S tiles are issued in the slots where
+        // S(j+1) would go and the tensor pipe never drains at an item boundary.
+        auto next_active = [&](Cursor& cur, Item& it) {     // advance to the next item that has keys
+            for (next_item(cur); cur.level >= 0; next_item(cur)) {
+                it = decode(cur);
+                if (it.ntiles > 0) return true;
             }
-            if (leader) tc5::commit(bar(O_DONE));
+            return false;
+        };
+#ifdef B200MOPS_TC5_TRACE
+        long long acct[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const long long t_begin = clock64();
+#endif
+        Cursor cur = first_item();
+        Item it{};
+        bool have = false;
+        for (; cur.level >= 0; next_item(cur)) {
+            it = decode(cur);
+            if (it.ntiles > 0) { have = true; break; }
         }
+        int g = 0, n_act = 0;       // index of the current tile in the stream, items finished
+        bool ok = have;
+        if (ok) ok = wait(Q_FULL, 0) && wait(K_FULL + 0, 0);
+        if (ok) {
+            tc5::fence_after_sync();
+            issue_s(0, 0);
+            issue_s(1, 0);
+            if (leader) {
+                tc5::commit(bar(K_EMPTY + 0));
+                if (it.ntiles == 1) tc5::commit(bar(Q_EMPTY));   // Q is free once its last S is issued
+            }
+        }
+        int j = 0;                  // tile index inside the current item
+        while (ok) {
+            const int s = g % kKVStages, sn = (g + 1) % kKVStages;
+            const bool last = j + 1 == it.ntiles;
+            const uint32_t acc0 = j > 0 ? 1u : 0u;
+            // what follows this tile in the stream
+            Cursor ncur = cur;
+            Item nit = it;
+            bool more = true, new_item = false;
+            if (last) {
+                more = next_active(ncur, nit);
+                new_item = more;
+            }
+            const int nj = last ? 0 : j + 1;
+            const bool next_is_last = more && (nj + 1 == nit.ntiles);
+            TC5_ACCT(2, ok = wait(V_FULL + s, g / kKVStages));
+            if (!ok) break;
+            // the previous item's epilogue must have lifted O out of TMEM before PV(0) lands
+            if (j == 0 && n_act > 0) TC5_ACCT(3, ok = wait(O_FREE + 0, n_act - 1));
+            if (!ok) break;
+            TC5_ACCT(4, ok = wait(P_FULL + 0, g));
+            if (!ok) break;
+            tc5::fence_after_sync();
+            issue_pv(0, g, acc0);
+            if (last && leader) tc5::commit(bar(O_DONE + 0));
+            if (more) {
+                if (new_item) TC5_ACCT(5, ok = wait(Q_FULL, n_act + 1));
+                if (!ok) break;
+                TC5_ACCT(5, ok = wait(K_FULL + sn, (g + 1) / kKVStages));
+                if (!ok) break;
+                tc5::fence_after_sync();
+                issue_s(0, g + 1);
+            }
+            if (j == 0 && n_act > 0) TC5_ACCT(3, ok = wait(O_FREE + 1, n_act - 1));
+            if (!ok) break;
+            TC5_ACCT(6, ok = wait(P_FULL + 1, g));
+            if (!ok) break;
+            tc5::fence_after_sync();
+            issue_pv(1, g, acc0);
+            if (leader) {
+                tc5::commit(bar(V_EMPTY + s));
+                if (last) tc5::commit(bar(O_DONE + 1));
+            }
+            if (!more) break;
+            issue_s(1, g + 1);
+            if (leader) {
+                tc5::commit(bar(K_EMPTY + sn));
+                if (next_is_last) tc5::commit(bar(Q_EMPTY));
+            }
+            ++g;
+            j = nj;
+            if (new_item) {
+                ++n_act;
+                cur = ncur;
+                it = nit;
+            }
+        }
+#ifdef B200MOPS_TC5_TRACE
+        if (lane == 0 && blockIdx.x < 256) {
+            acct[0] = clock64() - t_begin;
+            acct[1] = g + 1;
+            acct[7] = n_act + 1;
+            for (int i = 0; i < 8; ++i) g_tc5_acct[blockIdx.x][i] = acct[i];
+        }
+#endif
     } else {
         // ------------------------------------------------------------ softmax groups
         const int t = warp >> 2;                        // tile / query head within the pair
@@ -251,143 +384,149 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
         const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
         const uint32_t tS = tmem + lane_base + t * kBN;
         const uint32_t tO = tmem + lane_base + 256 + t * kD;
-        const int qi = m0 + row;                        // sequence-local query index
-        const int lim = p.causal ? min(len_k - 1, qi + off) : len_k - 1;   // last visible key
         const float c = p.scale_log2;
-        float m_ref = -INFINITY, l = 0.f;
-        bool ok = true;
         uint32_t sv[kBN / 32][32];
-        for (int j = 0; j < ntiles; ++j) {
-            ok = mbar_wait(bar(S_FULL + t), (uint32_t)j & 1u, p.status);
-            if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-            if (threadIdx.x % 128 == 0) TC5_TRACE(t, j, 0);
-            tc5::fence_after_sync();
-            const int key0 = j * kBN;
-            const bool need_mask = key0 + kBN - 1 > lim;      // this row crosses its limit here
-            const bool warp_mask = __any_sync(0xffffffffu, need_mask);
-            // The whole S row (128 fp32) is pulled into registers with one wait: TMEM load
-            // latency is paid once per tile instead of once per chunk.
+        int g = 0, n_act = 0;
+        bool ok = true;
+        for (Cursor cur = first_item(); ok && cur.level >= 0; next_item(cur)) {
+            const Item it = decode(cur);
+            const int ntiles = it.ntiles;
+            const int qi = it.m0 + row;                 // sequence-local query index
+            const int lim = p.causal ? min(it.len_k - 1, qi + it.off) : it.len_k - 1;   // last visible key
+            T* orow = reinterpret_cast<T*>(p.out) + (int64_t)(it.q_begin + qi) * p.out_stride_t +
+                      (int64_t)(it.hq0 + t) * p.out_stride_h;
+            if (ntiles == 0) {                          // no keys at all: the rows are zeros
+                if (qi < it.len_q) {
 #pragma unroll
-            for (int cc = 0; cc < kBN / 32; ++cc) tc5::ld32(tS + cc * 32, sv[cc]);
-            tc5::wait_ld();
-            if (threadIdx.x % 128 == 0) TC5_TRACE(t, j, 1);
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-            if (warp_mask) {
+                    for (int i = 0; i < kD; i += 8) *reinterpret_cast<uint4*>(orow + i) = make_uint4(0, 0, 0, 0);
+                }
+                continue;
+            }
+            float m_ref = -INFINITY, l = 0.f;
+            for (int j = 0; j < ntiles; ++j) {
+                ok = mbar_wait(bar(S_FULL + t), (uint32_t)(g + j) & 1u, p.status);
+                if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+                tc5::fence_after_sync();
+                const int key0 = j * kBN;
+                const bool need_mask = key0 + kBN - 1 > lim;      // this row crosses its limit here
+                const bool warp_mask = __any_sync(0xffffffffu, need_mask);
+                // The whole S row (128 fp32) is pulled into registers with one wait: TMEM load
+                // latency is paid once per tile instead of once per chunk.
+#pragma unroll
+                for (int cc = 0; cc < kBN / 32; ++cc) tc5::ld32(tS + cc * 32, sv[cc]);
+                tc5::wait_ld();
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+                if (warp_mask) {
+#pragma unroll
+                    for (int cc = 0; cc < kBN / 32; ++cc)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (key0 + cc * 32 + i > lim) sv[cc][i] = 0xff800000u;   // -inf
+                }
 #pragma unroll
                 for (int cc = 0; cc < kBN / 32; ++cc)
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (key0 + cc * 32 + i > lim) sv[cc][i] = 0xff800000u;   // -inf
-            }
-#pragma unroll
-            for (int cc = 0; cc < kBN / 32; ++cc)
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    mx0 = tc5::max3(mx0, __uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1]));
-                    mx1 = tc5::max3(mx1, __uint_as_float(sv[cc][i + 2]), __uint_as_float(sv[cc][i + 3]));
-                    mx2 = tc5::max3(mx2, __uint_as_float(sv[cc][i + 4]), __uint_as_float(sv[cc][i + 5]));
-                    mx3 = tc5::max3(mx3, __uint_as_float(sv[cc][i + 6]), __uint_as_float(sv[cc][i + 7]));
-                }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            const float m_new = fmaxf(m_ref, mx * c);
-            const bool grow = m_new > m_ref + kRescaleThreshold;   // also true for the first finite max
-            if (__any_sync(0xffffffffu, grow)) {
-                const float corr = grow ? fast_exp2(m_ref - m_new) : 1.f;   // exp2(-inf) = 0
-                if (j > 0) {
-                    // S(j) complete implies PV(j-1) complete (one thread issues both, in order),
-                    // so O_t is at rest until this group hands P(j) over.
+                    for (int i = 0; i < 32; i += 8) {
+                        mx0 = tc5::max3(mx0, __uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1]));
+                        mx1 = tc5::max3(mx1, __uint_as_float(sv[cc][i + 2]), __uint_as_float(sv[cc][i + 3]));
+                        mx2 = tc5::max3(mx2, __uint_as_float(sv[cc][i + 4]), __uint_as_float(sv[cc][i + 5]));
+                        mx3 = tc5::max3(mx3, __uint_as_float(sv[cc][i + 6]), __uint_as_float(sv[cc][i + 7]));
+                    }
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                const float m_new = fmaxf(m_ref, mx * c);
+                const bool grow = m_new > m_ref + kRescaleThreshold;   // also true for the first finite max
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float corr = grow ? fast_exp2(m_ref - m_new) : 1.f;   // exp2(-inf) = 0
+                    if (j > 0) {
+                        // S(j) complete implies PV(j-1) complete (one thread issues both, in order),
+                        // so O_t is at rest until this group hands P(j) over.
 #pragma unroll 1
-                    for (int cc = 0; cc < kD / 16; ++cc) {
-                        uint32_t ov[16];
-                        tc5::ld16(tO + cc * 16, ov);
-                        tc5::wait_ld();
+                        for (int cc = 0; cc < kD / 16; ++cc) {
+                            uint32_t ov[16];
+                            tc5::ld16(tO + cc * 16, ov);
+                            tc5::wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                        tc5::st16(tO + cc * 16, ov);
+                            for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                            tc5::st16(tO + cc * 16, ov);
+                        }
                     }
+                    l *= corr;
+                    if (grow) m_ref = m_new;
                 }
-                l *= corr;
-                if (grow) m_ref = m_new;
-            }
-            const float sub = m_ref == -INFINITY ? 0.f : m_ref;   // fully masked so far: stay finite
-            if (threadIdx.x % 128 == 0) TC5_TRACE(t, j, 2);
-            // P = exp2(S*c - m) (masked entries are -inf -> 0), row sum, 16-bit P into the S columns
-            // Packed fp32x2 arithmetic for the scale/subtract and the row sum; in tiles that need
-            // no mask three pairs in eight take the polynomial exp2 on the FMA pipe, which
-            // balances it against the special-function unit (masked entries must come out as
-            // exact zeros, which only ex2 gives, so masked tiles use ex2 throughout).
-            const tc5::f32x2 c2 = tc5::pack_f32x2(c, c), nsub2 = tc5::pack_f32x2(-sub, -sub);
-            tc5::f32x2 lsum = tc5::pack_f32x2(0.f, 0.f);
-            auto p_chunk = [&](int cc, auto use_poly) {
-                uint32_t pk[16];
+                const float sub = m_ref == -INFINITY ? 0.f : m_ref;   // fully masked so far: stay finite
+                // P = exp2(S*c - m) (masked entries are -inf -> 0), row sum, 16-bit P into the S columns
+                // Packed fp32x2 arithmetic for the scale/subtract and the row sum; in tiles that need
+                // no mask three pairs in eight take the polynomial exp2 on the FMA pipe, which
+                // balances it against the special-function unit (masked entries must come out as
+                // exact zeros, which only ex2 gives, so masked tiles use ex2 throughout).
+                const tc5::f32x2 c2 = tc5::pack_f32x2(c, c), nsub2 = tc5::pack_f32x2(-sub, -sub);
+                tc5::f32x2 lsum = tc5::pack_f32x2(0.f, 0.f);
+                auto p_chunk = [&](int cc, auto use_poly) {
+                    uint32_t pk[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const tc5::f32x2 x = tc5::fma2(
-                        tc5::pack_f32x2(__uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1])), c2, nsub2);
-                    float p0, p1;
-                    const int k8 = (i >> 1) & 7;
-                    if (decltype(use_poly)::value && ((kPolyMask >> k8) & 1)) {
-                        tc5::poly_exp2_x2(x, p0, p1);
-                    } else {
-                        float x0, x1;
-                        tc5::unpack_f32x2(x, x0, x1);
-                        p0 = fast_exp2(x0);
-                        p1 = fast_exp2(x1);
+                    for (int i = 0; i < 32; i += 2) {
+                        const tc5::f32x2 x = tc5::fma2(
+                            tc5::pack_f32x2(__uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1])), c2, nsub2);
+                        float p0, p1;
+                        const int k8 = (i >> 1) & 7;
+                        if (decltype(use_poly)::value && ((kPolyMask >> k8) & 1)) {
+                            tc5::poly_exp2_x2(x, p0, p1);
+                        } else {
+                            float x0, x1;
+                            tc5::unpack_f32x2(x, x0, x1);
+                            p0 = fast_exp2(x0);
+                            p1 = fast_exp2(x1);
+                        }
+                        lsum = tc5::add2(lsum, tc5::pack_f32x2(p0, p1));
+                        pk[i >> 1] = pack2<T>(p0, p1);
                     }
-                    lsum = tc5::add2(lsum, tc5::pack_f32x2(p0, p1));
-                    pk[i >> 1] = pack2<T>(p0, p1);
-                }
-                tc5::st16(tS + cc * 16, pk);
-            };
-            if (warp_mask) {
+                    tc5::st16(tS + cc * 16, pk);
+                };
+                if (warp_mask) {
 #pragma unroll
-                for (int cc = 0; cc < kBN / 32; ++cc) p_chunk(cc, std::false_type{});
-            } else {
-#pragma unroll
-                for (int cc = 0; cc < kBN / 32; ++cc) p_chunk(cc, std::true_type{});
-            }
-            tc5::wait_st();
-            tc5::fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar(P_FULL + t));
-            if (threadIdx.x % 128 == 0) TC5_TRACE(t, j, 3);
-            {
-                float l0, l1;
-                tc5::unpack_f32x2(lsum, l0, l1);
-                l += l0 + l1;
-            }
-        }
-        // ------------------------------------------------------------ epilogue
-        if (ok && ntiles > 0) {
-            ok = mbar_wait(bar(O_DONE), 0, p.status);
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) {
-            tc5::fence_after_sync();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            T* orow = reinterpret_cast<T*>(p.out) + (int64_t)(q_begin + qi) * p.out_stride_t +
-                      (int64_t)(hq0 + t) * p.out_stride_h;
-#pragma unroll
-            for (int cc = 0; cc < kD / 32; ++cc) {
-                if (ntiles > 0) {
-                    tc5::ld32(tO + cc * 32, sv[0]);
-                    tc5::wait_ld();
+                    for (int cc = 0; cc < kBN / 32; ++cc) p_chunk(cc, std::false_type{});
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) sv[0][i] = 0u;
+                    for (int cc = 0; cc < kBN / 32; ++cc) p_chunk(cc, std::true_type{});
                 }
-                if (qi < len_q) {
+                tc5::wait_st();
+                tc5::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(P_FULL + t));
+                {
+                    float l0, l1;
+                    tc5::unpack_f32x2(lsum, l0, l1);
+                    l += l0 + l1;
+                }
+            }
+            if (!ok) break;
+            // ---------------------------------------------------------- epilogue of the item
+            ok = mbar_wait(bar(O_DONE + t), (uint32_t)n_act & 1u, p.status);
+            if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+            tc5::fence_after_sync();
+#pragma unroll
+            for (int cc = 0; cc < kD / 32; ++cc) tc5::ld32(tO + cc * 32, sv[cc]);
+            tc5::wait_ld();
+            // O is in registers: the next item's first PV may overwrite it in TMEM
+            tc5::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(O_FREE + t));
+            if (qi < it.len_q) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+                for (int cc = 0; cc < kD / 32; ++cc)
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 w;
-                        w.x = pack2<T>(__uint_as_float(sv[0][i]) * inv, __uint_as_float(sv[0][i + 1]) * inv);
-                        w.y = pack2<T>(__uint_as_float(sv[0][i + 2]) * inv, __uint_as_float(sv[0][i + 3]) * inv);
-                        w.z = pack2<T>(__uint_as_float(sv[0][i + 4]) * inv, __uint_as_float(sv[0][i + 5]) * inv);
-                        w.w = pack2<T>(__uint_as_float(sv[0][i + 6]) * inv, __uint_as_float(sv[0][i + 7]) * inv);
+                        w.x = pack2<T>(__uint_as_float(sv[cc][i]) * inv, __uint_as_float(sv[cc][i + 1]) * inv);
+                        w.y = pack2<T>(__uint_as_float(sv[cc][i + 2]) * inv, __uint_as_float(sv[cc][i + 3]) * inv);
+                        w.z = pack2<T>(__uint_as_float(sv[cc][i + 4]) * inv, __uint_as_float(sv[cc][i + 5]) * inv);
+                        w.w = pack2<T>(__uint_as_float(sv[cc][i + 6]) * inv, __uint_as_float(sv[cc][i + 7]) * inv);
                         *reinterpret_cast<uint4*>(orow + cc * 32 + i) = w;
                     }
-                }
             }
+            g += ntiles;
+            ++n_act;
         }
     }
 
@@ -404,8 +543,8 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
 }  // namespace
 
 #ifdef B200MOPS_TC5_TRACE
-extern "C" int b200mops_debug_tc5_trace(long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, g_tc5_trace, sizeof(g_tc5_trace)) == cudaSuccess ? 0 : 1;
+extern "C" int b200mops_debug_tc5_acct(long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, g_tc5_acct, sizeof(g_tc5_acct)) == cudaSuccess ? 0 : 1;
 }
 #endif
 
@@ -414,12 +553,22 @@ int launch_varlen_prefill_tc5(const b200mops_varlen_prefill_args* a, const CUten
     Tc5Params p;
     p.out = a->out; p.out_stride_t = a->out_stride_t; p.out_stride_h = a->out_stride_h;
     p.cu_q = a->cu_seqlens_q; p.cu_k = a->cu_seqlens_k;
+    p.batch = (int)a->batch;
+    p.pairs = (int)(a->hq / 2);
+    p.levels = (int)((a->max_seqlen_q + kBM - 1) / kBM);
     p.group = (int)(a->hq / a->hkv);
     p.causal = a->causal ? 1 : 0;
     p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
     p.status = a->status_word;
-    const dim3 grid((unsigned)((a->max_seqlen_q + kBM - 1) / kBM), (unsigned)(a->hq / 2),
-                    (unsigned)a->batch);
+    // One CTA per SM; CTAs beyond the number of work items find an empty schedule and leave.
+    static int sm_count[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200MOPS_ERR_DEVICE;
+    if (sm_count[dev] == 0 &&
+        cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return B200MOPS_ERR_DEVICE;
+    const int64_t max_items = (int64_t)p.batch * p.pairs * p.levels;
+    const dim3 grid((unsigned)(max_items < sm_count[dev] ? max_items : sm_count[dev]));
     // Pairs (of every eight) whose exp2 runs as a polynomial on the FMA pipe instead of on the
     // special-function unit.  B200MOPS_TC5_POLY (0..4) overrides the default for measurements.
     static const int poly_pairs = [] {
@@ -447,7 +596,7 @@ int launch_varlen_prefill_tc5(const b200mops_varlen_prefill_args* a, const CUten
         B200MOPS_TC5_DISPATCH(__half)
     }
 #undef B200MOPS_TC5_DISPATCH
-    return launch_status();
+    return B200MOPS_ERR_DTYPE;
 }
 
 }  // namespace b200mops

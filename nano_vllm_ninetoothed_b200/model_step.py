@@ -1,0 +1,188 @@
+"""The caller side of the operator path: one Qwen3 decoder forward written against the `mops`
+operator surface, in the order nano-vLLM's model issues the calls
+(nanovllm/models/qwen3.py:74-82,140-153,167-177; nanovllm/layers/attention.py:24-43;
+nanovllm/layers/embed_head.py:37-68; nanovllm/layers/sampler.py:11-12).
+
+It exists to drive every operator in its real calling pattern -- strided q/k/v views of the
+fused qkv activation, q/k-norm on `[T, H, 128]` views, the two halves of gate_up, paged KV via
+slot_mapping / block_tables -- for end-to-end parity tests and for the decode tokens/s figure
+of the benchmark.  `ops` is any module with the mops names (this package's `mops`, or the CPU
+checker in tests), so the same function runs on both sides of a parity test.  Tensor
+parallelism follows the reference: heads, KV heads, intermediate and vocabulary are split
+over the ranks; the all-reduce after o_proj / down_proj / embedding and the logits gather are
+`torch.distributed` calls made here, outside the operators.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class Qwen3Config:
+    hidden: int = 1024
+    layers: int = 28
+    heads: int = 16
+    kv_heads: int = 8
+    head_dim: int = 128
+    intermediate: int = 3072
+    vocab: int = 151936
+    eps: float = 1e-6
+    rope_theta: float = 1000000.0
+    max_position: int = 4096
+    page: int = 256
+
+
+@dataclass
+class StepContext:
+    """Per-step metadata, as nanovllm/utils/context.py carries it."""
+    is_prefill: bool
+    slot_mapping: torch.Tensor
+    cu_seqlens: torch.Tensor | None = None      # prefill
+    max_seqlen: int = 0                         # prefill
+    context_lens: torch.Tensor | None = None    # decode
+    block_tables: torch.Tensor | None = None    # decode
+
+
+@dataclass
+class Qwen3Weights:
+    embed: torch.Tensor                 # [vocab / tp, hidden]
+    layers: list[dict] = field(default_factory=list)
+    final_norm: torch.Tensor | None = None
+    cos_sin: torch.Tensor | None = None         # [max_position, 1, head_dim] fp32
+
+
+def tp_info() -> tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return 0, 1
+
+
+def make_weights(cfg: Qwen3Config, seed: int = 0, dtype=torch.bfloat16, device="cpu",
+                 rank: int = 0, world: int = 1) -> Qwen3Weights:
+    """Random-init N(0, 0.02) weights (norm weights N(1, 0.02)).  The full tensors are drawn
+    from one seeded CPU stream and each rank keeps its shard, so any TP degree computes the
+    same model."""
+    g = torch.Generator().manual_seed(seed)
+
+    def rnd(*shape, std=0.02, mean=0.0):
+        return (torch.randn(*shape, generator=g) * std + mean).to(dtype)
+
+    def shard_rows(w, parts=1):
+        # rows are `parts` equal blocks (q|k|v or gate|up); each block is split over the ranks
+        blocks = w.chunk(parts, 0) if parts > 1 else (w,)
+        return torch.cat([b.chunk(world, 0)[rank] for b in blocks], 0)
+
+    hq, hkv, d = cfg.heads, cfg.kv_heads, cfg.head_dim
+    embed = rnd(cfg.vocab, cfg.hidden).chunk(world, 0)[rank].contiguous().to(device)
+    layers = []
+    for _ in range(cfg.layers):
+        wq, wk, wv = rnd(hq * d, cfg.hidden), rnd(hkv * d, cfg.hidden), rnd(hkv * d, cfg.hidden)
+        qkv = torch.cat([wq.chunk(world, 0)[rank], wk.chunk(world, 0)[rank], wv.chunk(world, 0)[rank]], 0)
+        layers.append(dict(
+            input_norm=rnd(cfg.hidden, mean=1.0).to(device),
+            qkv=qkv.contiguous().to(device),
+            q_norm=rnd(d, mean=1.0).to(device),
+            k_norm=rnd(d, mean=1.0).to(device),
+            o_proj=rnd(cfg.hidden, hq * d).chunk(world, 1)[rank].contiguous().to(device),
+            post_norm=rnd(cfg.hidden, mean=1.0).to(device),
+            gate_up=shard_rows(rnd(2 * cfg.intermediate, cfg.hidden), parts=2).contiguous().to(device),
+            down=rnd(cfg.hidden, cfg.intermediate).chunk(world, 1)[rank].contiguous().to(device),
+        ))
+    final_norm = rnd(cfg.hidden, mean=1.0).to(device)
+    inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float) / d))
+    freqs = torch.einsum("i,j->ij", torch.arange(cfg.max_position, dtype=torch.float), inv_freq)
+    cos_sin = torch.cat((freqs.cos(), freqs.sin()), dim=-1).unsqueeze(1).to(device)
+    return Qwen3Weights(embed, layers, final_norm, cos_sin)
+
+
+def allocate_kv_cache(cfg: Qwen3Config, num_blocks: int, dtype=torch.bfloat16, device="cpu",
+                      world: int = 1) -> torch.Tensor:
+    """One `[2, L, NB, page, Hkv/tp, d]` tensor; layers take views of it
+    (nanovllm/engine/model_runner.py:100-118)."""
+    return torch.zeros(2, cfg.layers, num_blocks, cfg.page, cfg.kv_heads // world, cfg.head_dim,
+                       dtype=dtype, device=device)
+
+
+def _all_reduce(x: torch.Tensor, world: int) -> torch.Tensor:
+    if world > 1:
+        dist.all_reduce(x)
+    return x
+
+
+def forward(ops, w: Qwen3Weights, cfg: Qwen3Config, kv_cache: torch.Tensor, input_ids: torch.Tensor,
+            positions: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    """Hidden states `[T, hidden]` after the final norm."""
+    rank, world = tp_info()
+    hq, hkv, d = cfg.heads // world, cfg.kv_heads // world, cfg.head_dim
+    q_size, kv_size = hq * d, hkv * d
+    scale = 1.0 / math.sqrt(d)
+    per = cfg.vocab // world
+    if world > 1:                       # vocab-parallel embedding (embed_head.py:37-45)
+        lo = per * rank
+        mask = (input_ids >= lo) & (input_ids < lo + per)
+        x = ops.embedding(mask * (input_ids - lo), w.embed)
+        x = _all_reduce(mask.unsqueeze(1) * x, world)
+    else:
+        x = ops.embedding(input_ids, w.embed)
+    cos, sin = w.cos_sin[positions].chunk(2, dim=-1)
+    residual = None
+    for li, lw in enumerate(w.layers):
+        if residual is None:
+            x, residual = ops.rms_forward(x, lw["input_norm"], cfg.eps), x
+        else:
+            x, residual = ops.add_rms_forward(x, residual, lw["input_norm"], cfg.eps)
+        qkv = ops.linear(x, lw["qkv"])
+        q, k, v = qkv.split([q_size, kv_size, kv_size], dim=-1)
+        q = ops.rms_forward(q.view(-1, hq, d), lw["q_norm"], cfg.eps)
+        k = ops.rms_forward(k.view(-1, hkv, d), lw["k_norm"], cfg.eps)
+        v = v.view(-1, hkv, d)
+        q = ops.apply_rotary_emb(q, cos, sin)
+        k = ops.apply_rotary_emb(k, cos, sin)
+        k_cache, v_cache = kv_cache[0, li], kv_cache[1, li]
+        ops.store_kvcache(k, v, k_cache, v_cache, ctx.slot_mapping)
+        if ctx.is_prefill:
+            o = ops.flash_attn_varlen_func(q, k, v, max_seqlen_q=ctx.max_seqlen,
+                                           cu_seqlens_q=ctx.cu_seqlens, max_seqlen_k=ctx.max_seqlen,
+                                           cu_seqlens_k=ctx.cu_seqlens, softmax_scale=scale,
+                                           causal=True, block_table=None)
+        else:
+            o = ops.flash_attn_with_kvcache(q.unsqueeze(1), k_cache, v_cache,
+                                            cache_seqlens=ctx.context_lens,
+                                            block_table=ctx.block_tables, softmax_scale=scale,
+                                            causal=True)
+        x = _all_reduce(ops.linear(o.flatten(1, -1) if ctx.is_prefill else o.reshape(-1, q_size),
+                                   lw["o_proj"]), world)
+        x, residual = ops.add_rms_forward(x, residual, lw["post_norm"], cfg.eps)
+        gate_up = ops.linear(x, lw["gate_up"])
+        a, b = gate_up.chunk(2, -1)
+        x = _all_reduce(ops.linear(ops.siluAndMul(a, b), lw["down"]), world)
+    x, _ = ops.add_rms_forward(x, residual, w.final_norm, cfg.eps)
+    return x
+
+
+def compute_logits(ops, w: Qwen3Weights, cfg: Qwen3Config, hidden: torch.Tensor,
+                   ctx: StepContext) -> torch.Tensor | None:
+    """Last token of each sequence -> logits `[B, vocab]` (gathered on rank 0 under TP)."""
+    rank, world = tp_info()
+    if ctx.is_prefill:
+        hidden = hidden[(ctx.cu_seqlens[1:] - 1).long()].contiguous()
+    logits = ops.linear(hidden, w.embed)
+    if world > 1:
+        parts = [torch.empty_like(logits) for _ in range(world)] if rank == 0 else None
+        dist.gather(logits, parts, 0)
+        logits = torch.cat(parts, -1) if rank == 0 else None
+    return logits
+
+
+def decode_step_inputs(context_lens: torch.Tensor, block_tables: torch.Tensor, page: int):
+    """positions and slot_mapping of a decode step, as model_runner.prepare_decode builds them:
+    the new token sits at position len-1, in the last live page of its sequence."""
+    lens = context_lens.long()
+    positions = lens - 1
+    last_page = block_tables.gather(1, ((lens - 1) // page).unsqueeze(1)).squeeze(1).long()
+    slots = (last_page * page + (lens - 1) % page).to(torch.int32)
+    return positions, slots

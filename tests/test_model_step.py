@@ -1,0 +1,118 @@
+"""The Qwen3 decoder forward that drives every operator in its real calling pattern: the CPU
+checker against itself (prefill vs prefill + decode), and the CUDA operators against the CPU
+checker on the same weights, inputs and KV-cache layout."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from nano_vllm_ninetoothed_b200 import model_step as M
+
+CFG = M.Qwen3Config(hidden=256, layers=2, heads=4, kv_heads=2, head_dim=128, intermediate=512,
+                    vocab=1000, max_position=1024, page=256)
+
+
+def _prefill_ctx(lens, tables, page, device="cpu"):
+    cu = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    cu[1:] = torch.tensor(lens).cumsum(0).to(torch.int32)
+    slots, pos = [], []
+    for b, n in enumerate(lens):
+        for i in range(n):
+            slots.append(int(tables[b, i // page]) * page + i % page)
+            pos.append(i)
+    ctx = M.StepContext(True, torch.tensor(slots, dtype=torch.int32, device=device),
+                        cu_seqlens=cu.to(device), max_seqlen=max(lens))
+    return ctx, torch.tensor(pos, dtype=torch.int64, device=device)
+
+
+def _run_prefill_then_decode(ops, device, lens, ids, next_ids):
+    w = M.make_weights(CFG, seed=3, device=device)
+    kv = M.allocate_kv_cache(CFG, num_blocks=8, device=device)
+    tables = torch.tensor([[3, 0], [5, 1], [2, 7]], dtype=torch.int32)
+    ctx, pos = _prefill_ctx(lens, tables, CFG.page, device)
+    h = M.forward(ops, w, CFG, kv, ids.to(device), pos, ctx)
+    logits_p = M.compute_logits(ops, w, CFG, h, ctx)
+    # one decode step for every sequence
+    clens = torch.tensor([n + 1 for n in lens], dtype=torch.int32, device=device)
+    tb = tables.to(device)
+    dpos, dslots = M.decode_step_inputs(clens, tb, CFG.page)
+    dctx = M.StepContext(False, dslots, context_lens=clens, block_tables=tb)
+    hd = M.forward(ops, w, CFG, kv, next_ids.to(device), dpos, dctx)
+    logits_d = M.compute_logits(ops, w, CFG, hd, dctx)
+    return logits_p, logits_d, kv
+
+
+def test_checker_decode_step_equals_prefill_of_the_longer_sequence():
+    from oracle import mops_oracle as O
+    g = torch.Generator().manual_seed(0)
+    lens = [5, 260, 31]
+    ids = torch.randint(0, CFG.vocab, (sum(lens),), generator=g)
+    nxt = torch.randint(0, CFG.vocab, (3,), generator=g)
+    _, logits_d, _ = _run_prefill_then_decode(O, "cpu", lens, ids, nxt)
+    # the same three sequences, each one token longer, as a single prefill
+    lens2 = [n + 1 for n in lens]
+    parts, cur = [], 0
+    for b, n in enumerate(lens):
+        parts += [ids[cur:cur + n], nxt[b:b + 1]]
+        cur += n
+    w = M.make_weights(CFG, seed=3)
+    kv = M.allocate_kv_cache(CFG, num_blocks=8)
+    tables = torch.tensor([[3, 0], [5, 1], [2, 7]], dtype=torch.int32)
+    ctx, pos = _prefill_ctx(lens2, tables, CFG.page)
+    h = M.forward(O, w, CFG, kv, torch.cat(parts), pos, ctx)
+    logits_full = M.compute_logits(O, w, CFG, h, ctx)
+    torch.testing.assert_close(logits_d.float(), logits_full.float(), atol=6e-2, rtol=5e-2)
+    assert torch.equal(logits_d.argmax(-1), logits_full.argmax(-1))
+
+
+@pytest.mark.gpu
+def test_cuda_operators_match_the_checker_through_the_whole_forward(mops):
+    from oracle import mops_oracle as O
+    g = torch.Generator().manual_seed(1)
+    lens = [129, 300, 7]
+    ids = torch.randint(0, CFG.vocab, (sum(lens),), generator=g)
+    nxt = torch.randint(0, CFG.vocab, (3,), generator=g)
+    want_p, want_d, kv_ref = _run_prefill_then_decode(O, "cpu", lens, ids, nxt)
+    got_p, got_d, kv = _run_prefill_then_decode(mops, "cuda:0", lens, ids, nxt)
+    # bf16 rounding differences compound over the layers; logits are O(1)
+    torch.testing.assert_close(got_p.float().cpu(), want_p.float(), atol=8e-2, rtol=5e-2)
+    torch.testing.assert_close(got_d.float().cpu(), want_d.float(), atol=8e-2, rtol=5e-2)
+    # layer-0 K/V rows come from identical inputs through rms_forward + rotary + store_kvcache
+    torch.testing.assert_close(kv[:, 0].float().cpu(), kv_ref[:, 0].float(), atol=2e-2, rtol=1e-2)
+    temps = torch.full((3,), 0.6)
+    tok_ref = O.sampler_forward(want_d, temps)
+    tok = mops.sampler_forward(got_d, temps.to("cuda:0")).cpu()
+    top2 = want_d.float().topk(2, -1).values
+    decisive = (top2[:, 0] - top2[:, 1]) > 0.1       # ignore near-ties between the two sides
+    assert torch.equal(tok[decisive], tok_ref[decisive])
+    assert mops.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_decode_step_is_cuda_graph_capturable(mops):
+    """The decode forward replays from a CUDA graph with refreshed inputs, as nano-vLLM's
+    capture_cudagraph path does (nanovllm/engine/model_runner.py:216-251)."""
+    dev = "cuda:0"
+    w = M.make_weights(CFG, seed=4, device=dev)
+    kv = M.allocate_kv_cache(CFG, num_blocks=8, device=dev)
+    kv.normal_()
+    tables = torch.tensor([[3, 0], [5, 1], [2, 7], [4, 6]], dtype=torch.int32, device=dev)
+    clens = torch.tensor([10, 300, 257, 0], dtype=torch.int32, device=dev)      # last row: padding
+    ids = torch.tensor([1, 2, 3, 0], device=dev)
+    pos, slots = M.decode_step_inputs(clens.clamp(min=1), tables, CFG.page)
+    slots[3] = -1
+    ctx = M.StepContext(False, slots, context_lens=clens, block_tables=tables)
+    eager = M.forward(mops, w, CFG, kv.clone(), ids, pos, ctx)
+    kv_g = kv.clone()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        M.forward(mops, w, CFG, kv_g.clone(), ids, pos, ctx)       # warm-up outside capture
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = M.forward(mops, w, CFG, kv_g, ids, pos, ctx)
+    graph.replay()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out[:3].float(), eager[:3].float(), atol=1e-2, rtol=1e-2)
+    assert mops.device_status() == 0
