@@ -11,30 +11,56 @@ namespace {
 constexpr int kThreads = 256;
 
 // ---------------------------------------------------------------- siluAndMul
+constexpr int kSiluUnroll = 4;   // independent 16-byte loads per operand per thread (vector path)
+
+template <typename T>
+__device__ __forceinline__ T silu_mul_one(T xv, T yv) {
+    // ex2-based exp and an approximate divide: their ~1e-6 relative error disappears in the
+    // rounding to the storage type, and the kernel stays bandwidth-bound instead of ALU-bound.
+    const float a = DType<T>::to_f32(xv);
+    const T act = DType<T>::from_f32(__fdividef(a, 1.f + __expf(-a)));
+    return DType<T>::from_f32(DType<T>::to_f32(act) * DType<T>::to_f32(yv));
+}
+
 template <typename T, bool kVec>
 __global__ void __launch_bounds__(kThreads)
 silu_mul_kernel(const T* __restrict__ x, const T* __restrict__ y, int64_t rows, int n,
                 int64_t x_stride0, int64_t y_stride0, T* __restrict__ out) {
-    constexpr int E = kVec ? Vec16<T>::kElems : 1;
-    const int per_row = n / E;
-    const int64_t idx = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-    if (idx >= rows * per_row) return;
-    const int64_t r = idx / per_row;
-    const int c = (int)(idx - r * per_row) * E;
-    auto f = [](T xv, T yv) {
-        const float a = DType<T>::to_f32(xv);
-        const T act = DType<T>::from_f32(__fdiv_rn(a, 1.f + expf(-a)));
-        return DType<T>::from_f32(DType<T>::to_f32(act) * DType<T>::to_f32(yv));
-    };
     if (kVec) {
-        const Vec16<T> xv = load16_stream(x + r * x_stride0 + c);
-        const Vec16<T> yv = load16_stream(y + r * y_stride0 + c);
-        Vec16<T> ov;
+        constexpr int E = Vec16<T>::kElems;
+        // 32-bit index arithmetic: the host launches at most 2^31 vectors per call of the kernel
+        const uint32_t per_row = (uint32_t)(n / E);
+        const uint32_t total = (uint32_t)rows * per_row;
+        const uint32_t base = blockIdx.x * (uint32_t)(kThreads * kSiluUnroll) + threadIdx.x;
+        Vec16<T> xv[kSiluUnroll], yv[kSiluUnroll];
+        uint32_t r[kSiluUnroll];
+        uint32_t c[kSiluUnroll];
 #pragma unroll
-        for (int e = 0; e < Vec16<T>::kElems; ++e) ov.v[e] = f(xv.v[e], yv.v[e]);
-        store16(out + r * (int64_t)n + c, ov);
+        for (int u = 0; u < kSiluUnroll; ++u) {
+            const uint32_t idx = base + (uint32_t)u * kThreads;
+            if (idx < total) {
+                r[u] = idx / per_row;
+                c[u] = (idx - r[u] * per_row) * E;
+                xv[u] = load16_stream(x + (int64_t)r[u] * x_stride0 + c[u]);
+                yv[u] = load16_stream(y + (int64_t)r[u] * y_stride0 + c[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kSiluUnroll; ++u) {
+            const uint32_t idx = base + (uint32_t)u * kThreads;
+            if (idx < total) {
+                Vec16<T> ov;
+#pragma unroll
+                for (int e = 0; e < E; ++e) ov.v[e] = silu_mul_one<T>(xv[u].v[e], yv[u].v[e]);
+                store16(out + (int64_t)r[u] * n + c[u], ov);
+            }
+        }
     } else {
-        out[r * (int64_t)n + c] = f(x[r * x_stride0 + c], y[r * y_stride0 + c]);
+        const int64_t idx = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+        if (idx >= rows * n) return;
+        const int64_t r = idx / n;
+        const int c = (int)(idx - r * n);
+        out[r * (int64_t)n + c] = silu_mul_one<T>(x[r * x_stride0 + c], y[r * y_stride0 + c]);
     }
 }
 
@@ -124,21 +150,42 @@ argmax_partial_kernel(const T* __restrict__ logits, int vocab, int64_t stride0,
     const float temp = __ldg(temperatures + r);
     const int begin = s * span, end = min(vocab, begin + span);
     Best b{-FLT_MAX, INT32_MAX};
+    // Dividing by a positive temperature is monotone, and two different 16-bit logits can never
+    // round to the same fp32 quotient, so for 16-bit inputs the comparison runs on the raw
+    // values; fp32 inputs (where neighbouring values could merge) keep the division.
+    const bool raw = sizeof(T) == 2 && temp > 0.f;
+    auto scaled = [&](T v) {
+        const float f = DType<T>::to_f32(v);
+        return raw ? f : __fdiv_rn(f, temp);
+    };
     const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) && (begin % E == 0);
     int scalar_from = begin;  // columns [scalar_from, end) are read one element at a time
     if (vec && end > begin) {
         const int n_full = (end - begin) / E;
-        for (int i = threadIdx.x; i < n_full; i += kThreads) {
+        int i = threadIdx.x;
+        for (; i + 3 * kThreads < n_full; i += 4 * kThreads) {     // four loads in flight
+            Vec16<T> v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = load16_stream(row + begin + (i + u * kThreads) * E);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int c = begin + (i + u * kThreads) * E;
+#pragma unroll
+                for (int e = 0; e < E; ++e)
+                    b = better(b, Best{scaled(v[u].v[e]), c + e});
+            }
+        }
+        for (; i < n_full; i += kThreads) {
             const int c = begin + i * E;
             const Vec16<T> v = load16_stream(row + c);
 #pragma unroll
             for (int e = 0; e < E; ++e)
-                b = better(b, Best{__fdiv_rn(DType<T>::to_f32(v.v[e]), temp), c + e});
+                b = better(b, Best{scaled(v.v[e]), c + e});
         }
         scalar_from = begin + n_full * E;
     }
     for (int c = scalar_from + threadIdx.x; c < end; c += kThreads)
-        b = better(b, Best{__fdiv_rn(DType<T>::to_f32(row[c]), temp), c});
+        b = better(b, Best{scaled(row[c]), c});
     b = block_best(b, smem);
     if (threadIdx.x == 0) {
         if (gridDim.x == 1) out[r] = b.idx == INT32_MAX ? 0 : b.idx;
@@ -161,8 +208,8 @@ argmax_final_kernel(const Best* __restrict__ partial, int splits, int64_t* __res
 
 int argmax_splits(int64_t rows, int64_t vocab) {
     if (rows <= 0) return 1;
-    int64_t s = (2 * kNumSMs + rows - 1) / rows;
-    const int64_t max_by_vocab = (vocab + 4095) / 4096;  // at least ~4k columns per block
+    int64_t s = (8 * kNumSMs + rows - 1) / rows;
+    const int64_t max_by_vocab = (vocab + 8191) / 8192;  // at least ~8k columns per block
     if (s > max_by_vocab) s = max_by_vocab;
     if (s > kMaxSplits) s = kMaxSplits;
     if (s < 1) s = 1;
@@ -185,12 +232,24 @@ extern "C" int b200mops_silu_mul(const void* x, const void* y, int64_t rows, int
         constexpr int E = Vec16<T>::kElems;
         const bool vec = n % E == 0 && x_stride0 % E == 0 && y_stride0 % E == 0 &&
                          aligned16(x) && aligned16(y) && aligned16(out);
-        const int64_t work = rows * (vec ? n / E : n);
-        const unsigned blocks = (unsigned)((work + kThreads - 1) / kThreads);
-        if (vec) silu_mul_kernel<T, true><<<blocks, kThreads, 0, as_stream(stream)>>>(
-            (const T*)x, (const T*)y, rows, (int)n, x_stride0, y_stride0, (T*)out);
-        else silu_mul_kernel<T, false><<<blocks, kThreads, 0, as_stream(stream)>>>(
-            (const T*)x, (const T*)y, rows, (int)n, x_stride0, y_stride0, (T*)out);
+        if (vec) {
+            // slices of at most 2^30 vectors keep the kernel's index arithmetic in 32 bits
+            const int64_t per_row = n / E;
+            const int64_t rows_per_launch = ((int64_t)1 << 30) / per_row > 0 ? ((int64_t)1 << 30) / per_row : 1;
+            for (int64_t r0 = 0; r0 < rows; r0 += rows_per_launch) {
+                const int64_t nr = rows - r0 < rows_per_launch ? rows - r0 : rows_per_launch;
+                const int64_t work = nr * per_row;
+                const unsigned blocks = (unsigned)((work + kThreads * kSiluUnroll - 1) / (kThreads * kSiluUnroll));
+                silu_mul_kernel<T, true><<<blocks, kThreads, 0, as_stream(stream)>>>(
+                    (const T*)x + r0 * x_stride0, (const T*)y + r0 * y_stride0, nr, (int)n, x_stride0,
+                    y_stride0, (T*)out + r0 * n);
+            }
+        } else {
+            const int64_t work = rows * n;
+            const unsigned blocks = (unsigned)((work + kThreads - 1) / kThreads);
+            silu_mul_kernel<T, false><<<blocks, kThreads, 0, as_stream(stream)>>>(
+                (const T*)x, (const T*)y, rows, (int)n, x_stride0, y_stride0, (T*)out);
+        }
     });
     return launch_status();
 }
