@@ -46,6 +46,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int32_t
 #pragma unroll 1
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
+        // somebody else already gave up: the hand-off will never come, do not wait out our own limit
+        if (status_word &&
+            (*reinterpret_cast<volatile int32_t*>(status_word) & B200MOPS_DEV_WAIT_TIMEOUT))
+            return false;
         if (clock64() - t0 > kWaitCycleLimit) {
             if (status_word) atomicOr(status_word, B200MOPS_DEV_WAIT_TIMEOUT);
             return false;
