@@ -349,7 +349,7 @@ int auto_chunk(int64_t batch, int64_t hkv, int64_t page, int64_t max_blocks) {
     const int64_t target_ctas = (int64_t)kNumSMs * 2 * 4;
     int64_t chunk = (batch * hkv * max_len + target_ctas - 1) / target_ctas;
     if (chunk < 128) chunk = 128;
-    if (chunk > 1024) chunk = 1024;
+    if (chunk > 2048) chunk = 2048;   // measured: 2048 beats 1024 by ~1 % at 8 KV heads, ties at one
     chunk = round_up(chunk, kTile);
     if (chunk >= max_len) chunk = round_up(max_len, kTile);
     return (int)chunk;

@@ -25,6 +25,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--chunk", type=int, default=0)
+    ap.add_argument("--graph", type=int, default=0, help="also time N back-to-back calls replayed as one CUDA graph")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
@@ -68,6 +69,21 @@ def main() -> None:
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
         print(f"{a.op} iter {i}: {ms:.4f} ms, {units:.4f} {unit} -> {units / (ms * 1e-3):.1f} {unit}/s")
+    if a.graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(a.graph):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / (5 * a.graph)
+        print(f"{a.op} graph x{a.graph}: {ms:.4f} ms per call -> {units / (ms * 1e-3):.1f} {unit}/s")
     assert mops.device_status() == 0
 
 
