@@ -1,0 +1,118 @@
+"""Seeded random shapes for the two attention operators and store_kvcache: each seed draws a
+batch, lengths (including 0 and 1), head grouping, page size, chunking, dtype and layout, and
+the CUDA result must match the CPU oracle within the 16-bit tolerance (bit-exact for the copy)."""
+from __future__ import annotations
+
+import random
+
+import pytest
+import torch
+
+from nano_vllm_ninetoothed_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOL = dict(atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_paged_decode(mops, oracle, seed):
+    rnd = random.Random(1000 + seed)
+    hkv = rnd.choice([1, 2, 4, 8])
+    g = rnd.choice([1, 2, 3, 4, 6, 8, 16])
+    page = rnd.choice([64, 128, 256])
+    batch = rnd.randint(1, 12)
+    top = rnd.choice([40, 300, 1500, 5000])
+    lens = [rnd.choice([0, 1, rnd.randint(1, top)]) if rnd.random() < 0.2 else rnd.randint(1, top)
+            for _ in range(batch)]
+    dtype = rnd.choice([torch.bfloat16, torch.bfloat16, torch.float16])
+    case = W.make_decode_case(seed=seed, lens=lens, hq=hkv * g, hkv=hkv, page=page, dtype=dtype,
+                              poison=True)
+    chunk = rnd.choice([0, 0, 64, 128, 320, 1024, 4096])
+    d = case.to(DEV)
+    got = mops.flash_attn_with_kvcache(d.q, d.k_cache, d.v_cache, cache_seqlens=d.cache_seqlens,
+                                       block_table=d.block_table, softmax_scale=d.softmax_scale,
+                                       causal=True, chunk_tokens=chunk)
+    want = oracle.flash_attn_with_kvcache(case.q, case.k_cache, case.v_cache,
+                                          cache_seqlens=case.cache_seqlens,
+                                          block_table=case.block_table.clamp(min=0),
+                                          softmax_scale=case.softmax_scale)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got.float().cpu(), want.float(), **TOL)
+    assert mops.device_status() == 0
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_varlen_prefill(mops, oracle, seed):
+    rnd = random.Random(2000 + seed)
+    hkv = rnd.choice([1, 2, 4])
+    g = rnd.choice([1, 2, 3, 4, 8])          # even groupings take the tcgen05 kernel, odd the mma.sync one
+    batch = rnd.randint(1, 7)
+    top = rnd.choice([20, 130, 400, 900])
+    lens = [rnd.randint(1, top) for _ in range(batch)]
+    dtype = rnd.choice([torch.bfloat16, torch.bfloat16, torch.float16])
+    causal = rnd.random() < 0.8
+    p = W.make_prefill_case(seed=seed, lens=lens, hq=hkv * g, hkv=hkv, dtype=dtype,
+                            strided_v=rnd.random() < 0.5)
+    d = p.to(DEV)
+    got = mops.flash_attn_varlen_func(d.q, d.k, d.v, max_seqlen_q=p.max_seqlen,
+                                      cu_seqlens_q=d.cu_seqlens, max_seqlen_k=p.max_seqlen,
+                                      cu_seqlens_k=d.cu_seqlens, softmax_scale=p.softmax_scale,
+                                      causal=causal)
+    want = oracle.flash_attn_varlen_func(p.q, p.k, p.v, p.cu_seqlens, p.cu_seqlens, p.max_seqlen,
+                                         p.max_seqlen, softmax_scale=p.softmax_scale, causal=causal)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got.float().cpu(), want.float(), **TOL)
+    assert mops.device_status() == 0
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_prefix_cache_prefill(mops, oracle, seed):
+    """Paged K/V with a cached prefix per sequence (cu_seqlens_k > cu_seqlens_q)."""
+    rnd = random.Random(3000 + seed)
+    hkv = rnd.choice([1, 2])
+    g = rnd.choice([1, 2, 4])
+    batch = rnd.randint(1, 5)
+    total = [rnd.randint(1, 900) for _ in range(batch)]
+    new = [rnd.randint(1, n) for n in total]
+    dec = W.make_decode_case(seed=seed, lens=total, hq=hkv * g, hkv=hkv, page=rnd.choice([64, 256]),
+                             poison=True)
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn(sum(new), hkv * g, 128, generator=gen).bfloat16()
+    cu_q = torch.tensor([0] + torch.tensor(new).cumsum(0).tolist(), dtype=torch.int32)
+    cu_k = torch.tensor([0] + torch.tensor(total).cumsum(0).tolist(), dtype=torch.int32)
+    want = oracle.flash_attn_varlen_func(q, dec.k_cache, dec.v_cache, cu_q, cu_k, max(new), max(total),
+                                         softmax_scale=dec.softmax_scale, causal=True,
+                                         block_table=dec.block_table.clamp(min=0))
+    d = dec.to(DEV)
+    got = mops.flash_attn_varlen_func(q.to(DEV), d.k_cache, d.v_cache, max_seqlen_q=max(new),
+                                      cu_seqlens_q=cu_q.to(DEV), max_seqlen_k=max(total),
+                                      cu_seqlens_k=cu_k.to(DEV), softmax_scale=dec.softmax_scale,
+                                      causal=True, block_table=d.block_table)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got.float().cpu(), want.float(), **TOL)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_store_kvcache(mops, oracle, seed):
+    rnd = random.Random(4000 + seed)
+    hkv = rnd.choice([1, 2, 4, 8])
+    n = rnd.randint(1, 3000)
+    blocks = (n + 255) // 256 + rnd.randint(0, 3)
+    dtype = rnd.choice([torch.bfloat16, torch.float16, torch.float32])
+    key, value, kc, vc, slots = W.make_store_case(seed=seed, n_tokens=n, hkv=hkv, num_blocks=blocks,
+                                                  dtype=dtype, strided=rnd.random() < 0.5,
+                                                  skip_every=rnd.choice([0, 3, 11]))
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    oracle.store_kvcache(key, value, kc_ref, vc_ref, slots)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    if key.is_contiguous():
+        k_dev, v_dev = key.to(DEV), value.to(DEV)
+    else:
+        base = key._base.to(DEV)
+        d = hkv * 128
+        k_dev = base[:, d:2 * d].view(n, hkv, 128)
+        v_dev = base[:, 2 * d:3 * d].view(n, hkv, 128)
+    mops.store_kvcache(k_dev, v_dev, kd, vd, slots.to(DEV))
+    assert torch.equal(kd.cpu(), kc_ref) and torch.equal(vd.cpu(), vc_ref)
