@@ -12,9 +12,9 @@ namespace b200mops {
 constexpr int kTc5MaxBatch = 1024;    // sequences per call
 constexpr int kTc5MaxLevels = 256;    // 128-row query tiles per sequence (max_seqlen_q <= 32768)
 
-// Launches the tcgen05/TMEM kernel.  Requirements checked by the caller: packed (non-paged)
-// K/V, head_dim 128, an even number of query heads per KV head, batch <= kTc5MaxBatch and
-// max_seqlen_q <= 128 * kTc5MaxLevels; the Q, K and V tensor maps carry 128-row boxes.
+// Launches the tcgen05/TMEM kernel.  Requirements checked by the caller: head_dim 128,
+// batch <= kTc5MaxBatch, max_seqlen_q <= 128 * kTc5MaxLevels, and for paged K/V a page size
+// that is a multiple of 128; the Q, K and V tensor maps carry 128-row boxes.
 int launch_varlen_prefill_tc5(const b200mops_varlen_prefill_args* a, const CUtensorMap& tm_q,
                               const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st);
 

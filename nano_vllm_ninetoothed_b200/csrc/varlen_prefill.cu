@@ -314,14 +314,14 @@ extern "C" int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* a, vo
     if (!aligned16(a->out) || (a->out_stride_t % 8) || (a->out_stride_h % 8))
         return B200MOPS_ERR_ALIGNMENT;
 
-    // Kernel choice: the tcgen05 kernel takes packed K/V with an even number of query heads per
-    // KV head; paged K/V (prefix-cache prefill) and odd groupings stay on the mma.sync kernel.
-    // B200MOPS_PREFILL_KERNEL=mma forces the latter (for A/B measurements).
+    // Kernel choice: the tcgen05 kernel takes everything except paged K/V whose page size is not
+    // a multiple of its 128-key tile and calls beyond its schedule-table capacity; those stay on
+    // the mma.sync kernel.  B200MOPS_PREFILL_KERNEL=mma forces the latter (for A/B measurements).
     static const bool force_mma = [] {
         const char* e = getenv("B200MOPS_PREFILL_KERNEL");
         return e != nullptr && strcmp(e, "mma") == 0;
     }();
-    const bool use_tc5 = !paged && ((a->hq / a->hkv) % 2 == 0) && !force_mma &&
+    const bool use_tc5 = !(paged && a->page % 128 != 0) && !force_mma &&
                          a->batch <= kTc5MaxBatch && a->max_seqlen_q <= (int64_t)128 * kTc5MaxLevels;
     const uint32_t kv_box_rows = use_tc5 ? 128u : (uint32_t)kBN;
 

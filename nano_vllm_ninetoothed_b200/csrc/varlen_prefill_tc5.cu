@@ -1,15 +1,21 @@
 // Variable-length causal prefill attention on the Blackwell tensor cores (tcgen05 + TMEM).
 //
 // Persistent kernel: one CTA per SM walks a static, heaviest-first list of work items.  A work
-// item is one 128-row query tile of one sequence for TWO query heads that share a KV head
-// (G = hq/hkv must be even), so every K/V tile fetched serves two S tiles, both tiles have the
-// same causal extent, and one tile's MMAs run while the other tile is in softmax.
+// item is a PAIR of 128-row query tiles that read the same K/V tiles, so every K/V tile fetched
+// serves two S tiles and one tile's MMAs run while the other tile is in softmax.  With an even
+// number of query heads per KV head the pair is one row tile of two neighbouring query heads
+// (same causal extent); with an odd number (MHA, G = 3, 5, ...) it is two consecutive row tiles
+// of one query head (the earlier tile sees its last KV tile fully masked; a second tile that
+// lies wholly past the sequence end is carried along without softmax work).
 //
-//   warps 0-3  softmax group 0 (query head 2p)     one thread per query row == TMEM lane
-//   warps 4-7  softmax group 1 (query head 2p+1)
+//   warps 0-3  softmax group 0 (first tile of the pair)   one thread per query row == TMEM lane
+//   warps 4-7  softmax group 1 (second tile of the pair)
 //   warp  8    MMA issuer: the warp runs the loop uniformly, one elected lane issues every
 //              tcgen05.mma / tcgen05.commit
-//   warp  9    TMA producer: Q tiles per item, 128-key K and V tiles through 2-stage rings
+//   warp  9    TMA producer: Q tiles per item, 128-key K and V tiles through 2-stage rings;
+//              K/V come from the packed tensors or, with a block table, from the paged caches
+//              (one page lookup per tile; the dead slots of a sequence's last page are zeroed
+//              in the V tile before the MMA warp may read it)
 //
 //   TMEM (512 columns x 128 lanes, fp32):  S0 [0,128)  S1 [128,256)  O0 [256,384)  O1 [384,512)
 //   P (16-bit) overwrites the first 64 columns of its S tile and is read by the PV MMA
@@ -34,7 +40,6 @@
 // Every mbarrier wait is bounded; on a timeout the roles fall through to the common exit,
 // which frees the tensor memory.
 #include <math.h>
-#include <stdlib.h>
 
 #include <type_traits>
 
@@ -61,8 +66,8 @@ constexpr int kOffK = kOffQ + 2 * kTileBytes;              // kKVStages tiles
 constexpr int kOffV = kOffK + kKVStages * kTileBytes;
 constexpr int kOffBar = kOffV + kKVStages * kTileBytes;
 // barriers: q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2],
-//           o_done[2], o_free[2]
-constexpr int kNumBars = 2 + 4 * kKVStages + 2 + 2 + 2 + 2;
+//           o_done[2], o_free[2], v_land
+constexpr int kNumBars = 2 + 4 * kKVStages + 2 + 2 + 2 + 2 + 1;
 constexpr int kOffSched = kOffBar + kNumBars * 8 + 16;     // schedule tables (uint16)
 constexpr int kSchedBytes = (2 * kTc5MaxBatch + kTc5MaxLevels) * 2;
 constexpr int kSmemBytes = 1024 + kOffSched + kSchedBytes;
@@ -84,6 +89,8 @@ __device__ long long g_tc5_acct[256][8];
 struct Tc5Params {
     void* out; int64_t out_stride_t, out_stride_h;
     const int32_t* cu_q; const int32_t* cu_k;
+    const int32_t* table; int64_t table_stride;     // block table (null: packed K/V)
+    int page, num_blocks;
     int batch, pairs, levels, group, causal;
     float scale_log2;
     int32_t* status;
@@ -91,16 +98,21 @@ struct Tc5Params {
 
 // One work item, as every role decodes it.
 struct Item {
-    int hq0, hk, q_begin, len_q, k_begin, len_k, m0, off, ntiles;
+    int b, hq0, hk, q_begin, len_q, k_begin, len_k, m0, off, ntiles;
 };
 
-// Position in the static schedule: `level` = row-tile index, `pos` = index inside the level
-// (sequence rank * pairs + pair).  Each CTA starts at its block index and strides by the grid.
+// Position in the static schedule: `level` = index of the item's row range in its sequence,
+// `pos` = index inside the level (sequence rank * pairs + pair).  Each CTA starts at its block index and strides by the grid.
 struct Cursor {
     int level, pos;
 };
 
-template <typename T, int kPolyMask>
+// kRowPair selects how the two tiles of an item relate: false = two query heads, same rows;
+// true = one query head, two consecutive row tiles.  kPaged: K/V come through a block table.
+// (Both are compile-time so that the packed, head-pair kernel carries no trace of the others:
+// register allocation is per kernel, and the producer's paged branch costs the softmax warps
+// registers otherwise.)
+template <typename T, int kPolyMask, bool kRowPair, bool kPaged>
 __global__ void __launch_bounds__(kThreads, 1)
 varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
                           const __grid_constant__ CUtensorMap tm_k,
@@ -119,21 +131,25 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
     constexpr int Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = K_FULL + kKVStages,
                   V_FULL = K_EMPTY + kKVStages, V_EMPTY = V_FULL + kKVStages,
                   S_FULL = V_EMPTY + kKVStages, P_FULL = S_FULL + 2, O_DONE = P_FULL + 2,
-                  O_FREE = O_DONE + 2;
+                  O_FREE = O_DONE + 2, V_LAND = O_FREE + 2;
 
     // Once any CTA has given up on a wait, the rest leave at once instead of each spending
     // its own time limit.
     if (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & B200MOPS_DEV_WAIT_TIMEOUT)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kHStep = kRowPair ? 0 : 1;            // second tile: head + kHStep,
+    constexpr int kMStep = kRowPair ? kBM : 0;          //              rows + kMStep
+    constexpr int kItemRows = kBM + kMStep;             // query rows one item covers
 
     // ---------------------------------------------------------------- schedule tables
     for (int b = threadIdx.x; b < p.batch; b += kThreads) {
         const int lq = __ldg(p.cu_q + b + 1) - __ldg(p.cu_q + b);
-        sched_mt[b] = (uint16_t)min(p.levels, max(0, (lq + kBM - 1) / kBM));
+        sched_mt[b] = (uint16_t)min(p.levels, max(0, (lq + kItemRows - 1) / kItemRows));
     }
     if (threadIdx.x == 0) {
         mbar_init(bar(Q_FULL), 1);
         mbar_init(bar(Q_EMPTY), 1);
+        mbar_init(bar(V_LAND), 1);
         for (int s = 0; s < kKVStages; ++s) {
             mbar_init(bar(K_FULL + s), 1);
             mbar_init(bar(K_EMPTY + s), 1);
@@ -190,50 +206,101 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
     auto decode = [&](const Cursor& cur) {
         Item it;
         const int b = sched_order[cur.pos / p.pairs];
-        it.hq0 = (cur.pos % p.pairs) * 2;
+        it.b = b;
+        it.hq0 = (cur.pos % p.pairs) * (1 + kHStep);
         it.hk = it.hq0 / p.group;
         it.q_begin = __ldg(p.cu_q + b);
         it.len_q = __ldg(p.cu_q + b + 1) - it.q_begin;
         it.k_begin = __ldg(p.cu_k + b);
         it.len_k = __ldg(p.cu_k + b + 1) - it.k_begin;
-        it.m0 = cur.level * kBM;
+        it.m0 = cur.level * kItemRows;
         it.off = it.len_k - it.len_q;
         int n_end = it.len_k;
-        if (p.causal) n_end = min(it.len_k, it.m0 + kBM + it.off);
+        if (p.causal) n_end = min(it.len_k, min(it.len_q, it.m0 + kItemRows) + it.off);
         it.ntiles = n_end > 0 ? (n_end + kBN - 1) / kBN : 0;
         return it;
     };
 
     if (warp == kLoadWarp) {
         // ------------------------------------------------------------ TMA producer
+        // Packed K/V: lane 0 alone runs the loop.  Paged K/V: the whole warp runs it uniformly
+        // (lane 0 issues the copies) because where a sequence ends inside a tile all lanes zero
+        // the dead V rows.
         if (lane == 0) {
             tma_prefetch_desc(&tm_q);
             tma_prefetch_desc(&tm_k);
             tma_prefetch_desc(&tm_v);
-            int g = 0, n_act = 0;       // KV tiles and non-empty items handled so far
+        }
+        if (kPaged || lane == 0) {
+            auto wait = [&](int b, uint32_t parity) {
+                const bool done = mbar_wait(bar(b), parity & 1u, p.status);
+                if constexpr (kPaged) return (bool)__all_sync(0xffffffffu, done);
+                else return done;
+            };
+            const bool issuer = !kPaged || lane == 0;
+            int g = 0, n_act = 0, n_fix = 0;   // KV tiles, non-empty items, zero-fixed tiles so far
             bool ok = true;
             for (Cursor cur = first_item(); ok && cur.level >= 0; next_item(cur)) {
                 const Item it = decode(cur);
                 if (it.ntiles == 0) continue;
                 // the previous item's last S MMA has read the Q tiles
-                if (n_act > 0 && !(ok = mbar_wait(bar(Q_EMPTY), (uint32_t)(n_act - 1) & 1u, p.status))) break;
-                mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
-                for (int t = 0; t < 2; ++t) {
-                    const uint32_t dst = sbase + kOffQ + t * kTileBytes;
-                    tma_load_4d(dst, &tm_q, bar(Q_FULL), 0, it.hq0 + t, it.q_begin + it.m0, 0);
-                    tma_load_4d(dst + kHalf, &tm_q, bar(Q_FULL), 64, it.hq0 + t, it.q_begin + it.m0, 0);
+                if (n_act > 0 && !(ok = wait(Q_EMPTY, n_act - 1))) break;
+                if (issuer) {
+                    mbar_arrive_expect_tx(bar(Q_FULL), 2 * kTileBytes);
+                    for (int t = 0; t < 2; ++t) {
+                        const uint32_t dst = sbase + kOffQ + t * kTileBytes;
+                        const int head = it.hq0 + t * kHStep, row = it.q_begin + it.m0 + t * kMStep;
+                        tma_load_4d(dst, &tm_q, bar(Q_FULL), 0, head, row, 0);
+                        tma_load_4d(dst + kHalf, &tm_q, bar(Q_FULL), 64, head, row, 0);
+                    }
                 }
                 for (int j = 0; j < it.ntiles; ++j, ++g) {
                     const int s = g % kKVStages, round = g / kKVStages;
-                    const int row = it.k_begin + j * kBN;
-                    if (round > 0 && !(ok = mbar_wait(bar(K_EMPTY + s), (uint32_t)(round - 1) & 1u, p.status))) break;
-                    mbar_arrive_expect_tx(bar(K_FULL + s), kTileBytes);
-                    tma_load_4d(sbase + kOffK + s * kTileBytes, &tm_k, bar(K_FULL + s), 0, it.hk, row, 0);
-                    tma_load_4d(sbase + kOffK + s * kTileBytes + kHalf, &tm_k, bar(K_FULL + s), 64, it.hk, row, 0);
-                    if (round > 0 && !(ok = mbar_wait(bar(V_EMPTY + s), (uint32_t)(round - 1) & 1u, p.status))) break;
-                    mbar_arrive_expect_tx(bar(V_FULL + s), kTileBytes);
-                    tma_load_4d(sbase + kOffV + s * kTileBytes, &tm_v, bar(V_FULL + s), 0, it.hk, row, 0);
-                    tma_load_4d(sbase + kOffV + s * kTileBytes + kHalf, &tm_v, bar(V_FULL + s), 64, it.hk, row, 0);
+                    int row, blk = 0;
+                    if constexpr (kPaged) {
+                        const int tok = j * kBN, pg = tok / p.page;
+                        blk = __ldg(p.table + (int64_t)it.b * p.table_stride + pg);
+                        if ((blk < 0 || blk >= p.num_blocks) && p.status && lane == 0)
+                            atomicOr(p.status, B200MOPS_DEV_BAD_PAGE);   // the copy then reads zero fill
+                        row = tok - pg * p.page;
+                    } else {
+                        row = it.k_begin + j * kBN;
+                    }
+                    if (round > 0 && !(ok = wait(K_EMPTY + s, round - 1))) break;
+                    if (issuer) {
+                        mbar_arrive_expect_tx(bar(K_FULL + s), kTileBytes);
+                        tma_load_4d(sbase + kOffK + s * kTileBytes, &tm_k, bar(K_FULL + s), 0, it.hk, row, blk);
+                        tma_load_4d(sbase + kOffK + s * kTileBytes + kHalf, &tm_k, bar(K_FULL + s), 64, it.hk, row, blk);
+                    }
+                    if (round > 0 && !(ok = wait(V_EMPTY + s, round - 1))) break;
+                    const uint32_t vdst = sbase + kOffV + s * kTileBytes;
+                    const int live = it.len_k - j * kBN;          // rows of this tile inside the sequence
+                    if (!(kPaged && live < kBN)) {
+                        if (issuer) {
+                            mbar_arrive_expect_tx(bar(V_FULL + s), kTileBytes);
+                            tma_load_4d(vdst, &tm_v, bar(V_FULL + s), 0, it.hk, row, blk);
+                            tma_load_4d(vdst + kHalf, &tm_v, bar(V_FULL + s), 64, it.hk, row, blk);
+                        }
+                    } else {
+                        // Dead slots of the last page may hold anything (NaN bit patterns included)
+                        // and P = 0 does not cancel them: land the tile on a private barrier, zero
+                        // its dead rows, and only then publish the stage to the MMA warp.
+                        if (issuer) {
+                            mbar_arrive_expect_tx(bar(V_LAND), kTileBytes);
+                            tma_load_4d(vdst, &tm_v, bar(V_LAND), 0, it.hk, row, blk);
+                            tma_load_4d(vdst + kHalf, &tm_v, bar(V_LAND), 64, it.hk, row, blk);
+                        }
+                        if (!(ok = wait(V_LAND, n_fix))) break;
+                        ++n_fix;
+                        for (int idx = lane; idx < (kBN - live) * 16; idx += 32) {
+                            const int r = live + (idx >> 4), pk = idx & 15;
+                            const uint32_t a = swz128(vdst + (pk >> 3) * kHalf, r, pk & 7);
+                            asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(a), "r"(0u) : "memory");
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(V_FULL + s));
+                    }
                 }
                 ++n_act;
             }
@@ -379,7 +446,7 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
 #endif
     } else {
         // ------------------------------------------------------------ softmax groups
-        const int t = warp >> 2;                        // tile / query head within the pair
+        const int t = warp >> 2;                        // tile within the pair
         const int row = threadIdx.x & 127;              // query row in the tile == TMEM lane
         const uint32_t lane_base = (uint32_t)(32 * (warp & 3)) << 16;
         const uint32_t tS = tmem + lane_base + t * kBN;
@@ -391,10 +458,13 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
         for (Cursor cur = first_item(); ok && cur.level >= 0; next_item(cur)) {
             const Item it = decode(cur);
             const int ntiles = it.ntiles;
-            const int qi = it.m0 + row;                 // sequence-local query index
+            const int qi = it.m0 + t * kMStep + row;   // sequence-local query index
             const int lim = p.causal ? min(it.len_k - 1, qi + it.off) : it.len_k - 1;   // last visible key
             T* orow = reinterpret_cast<T*>(p.out) + (int64_t)(it.q_begin + qi) * p.out_stride_t +
-                      (int64_t)(it.hq0 + t) * p.out_stride_h;
+                      (int64_t)(it.hq0 + t * kHStep) * p.out_stride_h;
+            // A second row tile that starts past the sequence end has no rows to produce: it only
+            // keeps the barrier protocol in step (its S/P/O columns hold don't-care values).
+            const bool idle = kRowPair && it.m0 + t * kMStep >= it.len_q;
             if (ntiles == 0) {                          // no keys at all: the rows are zeros
                 if (qi < it.len_q) {
 #pragma unroll
@@ -407,6 +477,12 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
                 ok = mbar_wait(bar(S_FULL + t), (uint32_t)(g + j) & 1u, p.status);
                 if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
                 tc5::fence_after_sync();
+                if (idle) {
+                    tc5::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(P_FULL + t));
+                    continue;
+                }
                 const int key0 = j * kBN;
                 const bool need_mask = key0 + kBN - 1 > lim;      // this row crosses its limit here
                 const bool warp_mask = __any_sync(0xffffffffu, need_mask);
@@ -553,10 +629,14 @@ int launch_varlen_prefill_tc5(const b200mops_varlen_prefill_args* a, const CUten
     Tc5Params p;
     p.out = a->out; p.out_stride_t = a->out_stride_t; p.out_stride_h = a->out_stride_h;
     p.cu_q = a->cu_seqlens_q; p.cu_k = a->cu_seqlens_k;
+    p.table = a->block_table; p.table_stride = a->table_stride0;
+    p.page = (int)a->page; p.num_blocks = (int)a->num_blocks;
     p.batch = (int)a->batch;
-    p.pairs = (int)(a->hq / 2);
-    p.levels = (int)((a->max_seqlen_q + kBM - 1) / kBM);
     p.group = (int)(a->hq / a->hkv);
+    const bool row_pair = p.group % 2 != 0;
+    p.pairs = row_pair ? (int)a->hq : (int)(a->hq / 2);
+    const int item_rows = row_pair ? 2 * kBM : kBM;     // query rows one work item covers
+    p.levels = (int)((a->max_seqlen_q + item_rows - 1) / item_rows);
     p.causal = a->causal ? 1 : 0;
     p.scale_log2 = a->softmax_scale * 1.4426950408889634f;
     p.status = a->status_word;
@@ -570,11 +650,9 @@ int launch_varlen_prefill_tc5(const b200mops_varlen_prefill_args* a, const CUten
     const int64_t max_items = (int64_t)p.batch * p.pairs * p.levels;
     const dim3 grid((unsigned)(max_items < sm_count[dev] ? max_items : sm_count[dev]));
     // Pairs (of every eight) whose exp2 runs as a polynomial on the FMA pipe instead of on the
-    // special-function unit.  B200MOPS_TC5_POLY (0..4) overrides the default for measurements.
-    static const int poly_pairs = [] {
-        const char* e = getenv("B200MOPS_TC5_POLY");
-        return e ? atoi(e) : 3;
-    }();
+    // special-function unit: three (bits 1, 4 and 6), which balances the two pipes.
+    constexpr int kPoly = 0x52;
+    const bool paged = a->block_table != nullptr;
     auto launch = [&](auto kernel) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
             cudaSuccess)
@@ -583,13 +661,11 @@ int launch_varlen_prefill_tc5(const b200mops_varlen_prefill_args* a, const CUten
         return launch_status();
     };
 #define B200MOPS_TC5_DISPATCH(TYPE)                                                    \
-    switch (poly_pairs) {                                                              \
-        case 0: return launch(varlen_prefill_tc5_kernel<TYPE, 0x00>);                  \
-        case 1: return launch(varlen_prefill_tc5_kernel<TYPE, 0x10>);                  \
-        case 2: return launch(varlen_prefill_tc5_kernel<TYPE, 0x22>);                  \
-        case 4: return launch(varlen_prefill_tc5_kernel<TYPE, 0xAA>);                  \
-        default: return launch(varlen_prefill_tc5_kernel<TYPE, 0x52>);                 \
-    }
+    if (row_pair)                                                                      \
+        return paged ? launch(varlen_prefill_tc5_kernel<TYPE, kPoly, true, true>)      \
+                     : launch(varlen_prefill_tc5_kernel<TYPE, kPoly, true, false>);    \
+    return paged ? launch(varlen_prefill_tc5_kernel<TYPE, kPoly, false, true>)         \
+                 : launch(varlen_prefill_tc5_kernel<TYPE, kPoly, false, false>);
     if (a->dtype == B200MOPS_BF16) {
         B200MOPS_TC5_DISPATCH(__nv_bfloat16)
     } else {

@@ -181,7 +181,17 @@ def test_prefill_tile_boundaries_and_single_tokens(mops, oracle):
     run_prefill(mops, oracle, W.make_prefill_case(seed=1, lens=lens, hq=4, hkv=2))
 
 
-@pytest.mark.parametrize("hq,hkv", [(1, 1), (4, 1), (4, 4), (8, 2), (6, 2)])
+@pytest.mark.parametrize("hq,hkv", [(1, 1), (3, 1), (5, 5)])
+def test_prefill_tile_boundaries_odd_head_groups(mops, oracle, hq, hkv):
+    """Odd groupings pair two consecutive row tiles of one head: lengths on both sides of the
+    128- and 256-row boundaries, odd and even numbers of row tiles."""
+    lens = [1, 127, 128, 129, 255, 256, 257, 383, 384, 385, 511, 512, 513, 640, 769, 1]
+    run_prefill(mops, oracle, W.make_prefill_case(seed=4, lens=lens, hq=hq, hkv=hkv))
+    run_prefill(mops, oracle, W.make_prefill_case(seed=5, lens=lens[:9], hq=hq, hkv=hkv), causal=False)
+    assert mops.device_status() == 0
+
+
+@pytest.mark.parametrize("hq,hkv", [(1, 1), (4, 1), (4, 4), (8, 2), (6, 2), (10, 2)])
 def test_prefill_head_groupings(mops, oracle, hq, hkv):
     run_prefill(mops, oracle, W.make_prefill_case(seed=2, batch=4, len_lo=1, len_hi=400, hq=hq,
                                                   hkv=hkv, strided_v=True))
@@ -193,16 +203,19 @@ def test_prefill_non_causal_and_fp16(mops, oracle):
                                                   dtype=torch.float16))
 
 
-def test_prefill_with_block_table_prefix_cache(mops, oracle):
+@pytest.mark.parametrize("hq,hkv,page", [(8, 2, 256), (5, 1, 256), (3, 3, 256), (4, 2, 128),
+                                         (3, 1, 128), (8, 2, 64), (3, 1, 64)])
+def test_prefill_with_block_table_prefix_cache(mops, oracle, hq, hkv, page):
     """Prefix-cache prefill: new tokens attend to paged K/V that also hold a cached prefix;
-    causal mask aligned bottom-right; dead slots of the last page are NaN."""
+    causal mask aligned bottom-right; dead slots of the last page are NaN.  Even and odd head
+    groupings and page sizes on both sides of the 128-key tile of the tcgen05 kernel."""
     g = torch.Generator().manual_seed(9)
-    total_lens = [700, 256, 300, 1025]
-    new_lens = [188, 256, 44, 1]
-    dec = W.make_decode_case(seed=9, lens=total_lens, hq=8, hkv=2, poison=True)
+    total_lens = [700, 256, 300, 1025, 129, 640]
+    new_lens = [188, 256, 44, 1, 129, 385]
+    dec = W.make_decode_case(seed=9, lens=total_lens, hq=hq, hkv=hkv, page=page, poison=True)
     cu_q = torch.tensor([0] + list(torch.tensor(new_lens).cumsum(0)), dtype=torch.int32)
     cu_k = torch.tensor([0] + list(torch.tensor(total_lens).cumsum(0)), dtype=torch.int32)
-    q = torch.randn(sum(new_lens), 8, 128, generator=g).bfloat16()
+    q = torch.randn(sum(new_lens), hq, 128, generator=g).bfloat16()
     want = oracle.flash_attn_varlen_func(q, dec.k_cache, dec.v_cache, cu_q, cu_k, max(new_lens),
                                          max(total_lens), softmax_scale=dec.softmax_scale,
                                          causal=True, block_table=dec.block_table.clamp(min=0))
