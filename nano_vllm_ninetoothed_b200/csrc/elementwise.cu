@@ -158,6 +158,12 @@ argmax_partial_kernel(const T* __restrict__ logits, int vocab, int64_t stride0,
         const float f = DType<T>::to_f32(v);
         return raw ? f : __fdiv_rn(f, temp);
     };
+    // A thread visits its columns in ascending order, so "strictly greater" already keeps the
+    // lowest index among equal values; the index tie-break is only needed between threads.
+    auto take = [&](T v, int c) {
+        const float f = scaled(v);
+        if (f > b.val) b = Best{f, c};
+    };
     const bool vec = ((reinterpret_cast<uintptr_t>(row) & 15u) == 0) && (begin % E == 0);
     int scalar_from = begin;  // columns [scalar_from, end) are read one element at a time
     if (vec && end > begin) {
@@ -171,21 +177,18 @@ argmax_partial_kernel(const T* __restrict__ logits, int vocab, int64_t stride0,
             for (int u = 0; u < 4; ++u) {
                 const int c = begin + (i + u * kThreads) * E;
 #pragma unroll
-                for (int e = 0; e < E; ++e)
-                    b = better(b, Best{scaled(v[u].v[e]), c + e});
+                for (int e = 0; e < E; ++e) take(v[u].v[e], c + e);
             }
         }
         for (; i < n_full; i += kThreads) {
             const int c = begin + i * E;
             const Vec16<T> v = load16_stream(row + c);
 #pragma unroll
-            for (int e = 0; e < E; ++e)
-                b = better(b, Best{scaled(v.v[e]), c + e});
+            for (int e = 0; e < E; ++e) take(v.v[e], c + e);
         }
         scalar_from = begin + n_full * E;
     }
-    for (int c = scalar_from + threadIdx.x; c < end; c += kThreads)
-        b = better(b, Best{scaled(row[c]), c});
+    for (int c = scalar_from + threadIdx.x; c < end; c += kThreads) take(row[c], c);
     b = block_best(b, smem);
     if (threadIdx.x == 0) {
         if (gridDim.x == 1) out[r] = b.idx == INT32_MAX ? 0 : b.idx;
@@ -208,8 +211,10 @@ argmax_final_kernel(const Best* __restrict__ partial, int splits, int64_t* __res
 
 int argmax_splits(int64_t rows, int64_t vocab) {
     if (rows <= 0) return 1;
-    int64_t s = (8 * kNumSMs + rows - 1) / rows;
-    const int64_t max_by_vocab = (vocab + 8191) / 8192;  // at least ~8k columns per block
+    // About four waves of blocks (eight 256-thread blocks fit an SM), so that the last, partly
+    // filled wave is a small share of the run.
+    int64_t s = (32 * kNumSMs + rows - 1) / rows;
+    const int64_t max_by_vocab = (vocab + 4095) / 4096;  // at least ~4k columns per block
     if (s > max_by_vocab) s = max_by_vocab;
     if (s > kMaxSplits) s = kMaxSplits;
     if (s < 1) s = 1;

@@ -67,7 +67,8 @@ constexpr int kOffV = kOffK + kKVStages * kTileBytes;
 constexpr int kOffBar = kOffV + kKVStages * kTileBytes;
 // barriers: q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2],
 //           o_done[2], o_free[2], v_land
-constexpr int kNumBars = 2 + 4 * kKVStages + 2 + 2 + 2 + 2 + 1;
+constexpr int kPParts = 2;                // instalments in which a P tile is handed to the MMA warp
+constexpr int kNumBars = 2 + 4 * kKVStages + 2 + 2 * kPParts + 2 + 2 + 1;
 constexpr int kOffSched = kOffBar + kNumBars * 8 + 16;     // schedule tables (uint16)
 constexpr int kSchedBytes = (2 * kTc5MaxBatch + kTc5MaxLevels) * 2;
 constexpr int kSmemBytes = 1024 + kOffSched + kSchedBytes;
@@ -130,7 +131,7 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
     auto bar = [&](int i) { return bar0 + 8u * i; };
     constexpr int Q_FULL = 0, Q_EMPTY = 1, K_FULL = 2, K_EMPTY = K_FULL + kKVStages,
                   V_FULL = K_EMPTY + kKVStages, V_EMPTY = V_FULL + kKVStages,
-                  S_FULL = V_EMPTY + kKVStages, P_FULL = S_FULL + 2, O_DONE = P_FULL + 2,
+                  S_FULL = V_EMPTY + kKVStages, P_PART = S_FULL + 2, O_DONE = P_PART + 2 * kPParts,
                   O_FREE = O_DONE + 2, V_LAND = O_FREE + 2;
 
     // Once any CTA has given up on a wait, the rest leave at once instead of each spending
@@ -158,7 +159,8 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar(S_FULL + t), 1);
-            mbar_init(bar(P_FULL + t), 4);      // one arrival per softmax warp
+            for (int i = 0; i < kPParts; ++i)
+                mbar_init(bar(P_PART + t * kPParts + i), 4);      // one arrival per softmax warp
             mbar_init(bar(O_FREE + t), 4);
             mbar_init(bar(O_DONE + t), 1);
         }
@@ -337,14 +339,24 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
         };
         // O_t (+)= P_t V for ring tile g: 8 k-steps of 16 keys; A = P from TMEM, B = V MN-major
+        // P arrives in kPParts instalments of 128 / kPParts keys; each is multiplied as soon as it
+        // is there.  Returns false when a wait ran out.
         auto issue_pv = [&](int t, int g, uint32_t acc0) {
             const uint64_t b0 = dv + ((uint32_t)((g % kKVStages) * kTileBytes) >> 4);
-            if (leader) {
 #pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk)
-                    tc5::mma_ts(tm + 256 + t * kD, tm + t * kBN + kk * 8,
-                                b0 + (uint32_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : acc0);
+            for (int i = 0; i < kPParts; ++i) {
+                if (!wait(P_PART + t * kPParts + i, g)) return false;
+                tc5::fence_after_sync();
+                if (leader) {
+#pragma unroll
+                    for (int k4 = 0; k4 < kBN / 16 / kPParts; ++k4) {
+                        const int kk = i * (kBN / 16 / kPParts) + k4;
+                        tc5::mma_ts(tm + 256 + t * kD, tm + t * kBN + kk * 8,
+                                    b0 + (uint32_t)(kk * 2048 >> 4), idesc_o, kk > 0 ? 1u : acc0);
+                    }
+                }
             }
+            return true;
         };
         // The KV tiles of all items form one stream: the tile after an item's last tile is the
         // first tile of the next item, so the next item's S tiles are issued in the slots where
@@ -399,10 +411,8 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
             // the previous item's epilogue must have lifted O out of TMEM before PV(0) lands
             if (j == 0 && n_act > 0) TC5_ACCT(3, ok = wait(O_FREE + 0, n_act - 1));
             if (!ok) break;
-            TC5_ACCT(4, ok = wait(P_FULL + 0, g));
+            TC5_ACCT(4, ok = issue_pv(0, g, acc0));
             if (!ok) break;
-            tc5::fence_after_sync();
-            issue_pv(0, g, acc0);
             if (last && leader) tc5::commit(bar(O_DONE + 0));
             if (more) {
                 if (new_item) TC5_ACCT(5, ok = wait(Q_FULL, n_act + 1));
@@ -414,10 +424,8 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
             if (j == 0 && n_act > 0) TC5_ACCT(3, ok = wait(O_FREE + 1, n_act - 1));
             if (!ok) break;
-            TC5_ACCT(6, ok = wait(P_FULL + 1, g));
+            TC5_ACCT(6, ok = issue_pv(1, g, acc0));
             if (!ok) break;
-            tc5::fence_after_sync();
-            issue_pv(1, g, acc0);
             if (leader) {
                 tc5::commit(bar(V_EMPTY + s));
                 if (last) tc5::commit(bar(O_DONE + 1));
@@ -480,7 +488,9 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
                 if (idle) {
                     tc5::fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(P_FULL + t));
+                    if (lane == 0) {
+                        for (int i = 0; i < kPParts; ++i) mbar_arrive(bar(P_PART + t * kPParts + i));
+                    }
                     continue;
                 }
                 const int key0 = j * kBN;
@@ -558,17 +568,20 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
                     }
                     tc5::st16(tS + cc * 16, pk);
                 };
-                if (warp_mask) {
+                // P is handed over in instalments so that the PV MMAs of the first keys run while
+                // the exponentials of the later ones are still being computed.
 #pragma unroll
-                    for (int cc = 0; cc < kBN / 32; ++cc) p_chunk(cc, std::false_type{});
-                } else {
+                for (int i = 0; i < kPParts; ++i) {
 #pragma unroll
-                    for (int cc = 0; cc < kBN / 32; ++cc) p_chunk(cc, std::true_type{});
+                    for (int cc = i * (kBN / 32 / kPParts); cc < (i + 1) * (kBN / 32 / kPParts); ++cc) {
+                        if (warp_mask) p_chunk(cc, std::false_type{});
+                        else p_chunk(cc, std::true_type{});
+                    }
+                    tc5::wait_st();
+                    tc5::fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(P_PART + t * kPParts + i));
                 }
-                tc5::wait_st();
-                tc5::fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(P_FULL + t));
                 {
                     float l0, l1;
                     tc5::unpack_f32x2(lsum, l0, l1);
