@@ -211,10 +211,11 @@ argmax_final_kernel(const Best* __restrict__ partial, int splits, int64_t* __res
 
 int argmax_splits(int64_t rows, int64_t vocab) {
     if (rows <= 0) return 1;
-    // About four waves of blocks (eight 256-thread blocks fit an SM), so that the last, partly
-    // filled wave is a small share of the run.
-    int64_t s = (32 * kNumSMs + rows - 1) / rows;
-    const int64_t max_by_vocab = (vocab + 4095) / 4096;  // at least ~4k columns per block
+    // About one resident wave of blocks (eight 256-thread blocks fit an SM).  More, smaller blocks
+    // were measured slower (256 x 151936 bf16: 3 or 5 splits 24-25 us, 10 splits 31 us, 19 splits
+    // 38 us): the per-block reduction and launch cost outweighs the better tail.
+    int64_t s = (8 * kNumSMs + rows - 1) / rows;
+    const int64_t max_by_vocab = (vocab + 8191) / 8192;  // at least ~8k columns per block
     if (s > max_by_vocab) s = max_by_vocab;
     if (s > kMaxSplits) s = kMaxSplits;
     if (s < 1) s = 1;
