@@ -197,6 +197,16 @@ def test_prefill_head_groupings(mops, oracle, hq, hkv):
                                                   hkv=hkv, strided_v=True))
 
 
+@pytest.mark.parametrize("batch", [1024, 1100])
+def test_prefill_many_short_sequences(mops, oracle, batch):
+    """1024 sequences fill the tcgen05 kernel's schedule tables exactly; 1100 exceed them and take
+    the mma.sync kernel.  Lengths 1..40, so most query tiles are nearly empty."""
+    g = torch.Generator().manual_seed(batch)
+    lens = torch.randint(1, 41, (batch,), generator=g).tolist()
+    run_prefill(mops, oracle, W.make_prefill_case(seed=6, lens=lens, hq=4, hkv=2))
+    assert mops.device_status() == 0
+
+
 def test_prefill_non_causal_and_fp16(mops, oracle):
     run_prefill(mops, oracle, W.make_prefill_case(seed=3, lens=[50, 200, 129], hq=4, hkv=2), causal=False)
     run_prefill(mops, oracle, W.make_prefill_case(seed=3, lens=[50, 200, 129], hq=4, hkv=2,
