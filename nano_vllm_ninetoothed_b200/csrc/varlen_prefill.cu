@@ -315,14 +315,14 @@ extern "C" int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* a, vo
         return B200MOPS_ERR_ALIGNMENT;
 
     // Kernel choice: the tcgen05 kernel takes everything except paged K/V whose page size is not
-    // a multiple of its 128-key tile and calls beyond its schedule-table capacity; those stay on
+    // a multiple of its 128-key tile and sequences of more than 32768 query rows; those stay on
     // the mma.sync kernel.  B200MOPS_PREFILL_KERNEL=mma forces the latter (for A/B measurements).
     static const bool force_mma = [] {
         const char* e = getenv("B200MOPS_PREFILL_KERNEL");
         return e != nullptr && strcmp(e, "mma") == 0;
     }();
     const bool use_tc5 = !(paged && a->page % 128 != 0) && !force_mma &&
-                         a->batch <= kTc5MaxBatch && a->max_seqlen_q <= (int64_t)128 * kTc5MaxLevels;
+                         a->max_seqlen_q <= (int64_t)128 * kTc5MaxLevels;
     const uint32_t kv_box_rows = use_tc5 ? 128u : (uint32_t)kBN;
 
     CUtensorMap tm_q, tm_k, tm_v;
@@ -353,7 +353,20 @@ extern "C" int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* a, vo
         if (rc != B200MOPS_OK) return rc;
     }
 
-    if (use_tc5) return launch_varlen_prefill_tc5(a, tm_q, tm_k, tm_v, as_stream(stream));
+    if (use_tc5) {
+        // The kernel's schedule tables hold kTc5MaxBatch sequences: longer batches go in slices
+        // (cu_seqlens are absolute offsets, so a slice is the same call on a later window).
+        for (int64_t b0 = 0; b0 < a->batch; b0 += kTc5MaxBatch) {
+            b200mops_varlen_prefill_args part = *a;
+            part.batch = a->batch - b0 < kTc5MaxBatch ? a->batch - b0 : kTc5MaxBatch;
+            part.cu_seqlens_q = a->cu_seqlens_q + b0;
+            part.cu_seqlens_k = a->cu_seqlens_k + b0;
+            if (paged) part.block_table = a->block_table + b0 * a->table_stride0;
+            const int rc = launch_varlen_prefill_tc5(&part, tm_q, tm_k, tm_v, as_stream(stream));
+            if (rc != B200MOPS_OK) return rc;
+        }
+        return B200MOPS_OK;
+    }
 
     PrefillParams p;
     p.out = a->out; p.out_stride_t = a->out_stride_t; p.out_stride_h = a->out_stride_h;

@@ -199,11 +199,33 @@ def test_prefill_head_groupings(mops, oracle, hq, hkv):
 
 @pytest.mark.parametrize("batch", [1024, 1100])
 def test_prefill_many_short_sequences(mops, oracle, batch):
-    """1024 sequences fill the tcgen05 kernel's schedule tables exactly; 1100 exceed them and take
-    the mma.sync kernel.  Lengths 1..40, so most query tiles are nearly empty."""
+    """1024 sequences fill the tcgen05 kernel's schedule tables exactly; 1100 go in two launches.
+    Lengths 1..40, so most query tiles are nearly empty."""
     g = torch.Generator().manual_seed(batch)
     lens = torch.randint(1, 41, (batch,), generator=g).tolist()
     run_prefill(mops, oracle, W.make_prefill_case(seed=6, lens=lens, hq=4, hkv=2))
+    assert mops.device_status() == 0
+
+
+def test_prefill_many_short_sequences_paged(mops, oracle):
+    """1100 sequences over paged K/V: the second launch starts at row 1024 of the block table."""
+    g = torch.Generator().manual_seed(77)
+    batch = 1100
+    total = torch.randint(1, 200, (batch,), generator=g)
+    new = torch.minimum(total, torch.randint(1, 40, (batch,), generator=g))
+    dec = W.make_decode_case(seed=7, lens=total.tolist(), hq=4, hkv=2, page=128, poison=True)
+    cu_q = torch.cat([torch.zeros(1, dtype=torch.int64), new.cumsum(0)]).to(torch.int32)
+    cu_k = torch.cat([torch.zeros(1, dtype=torch.int64), total.cumsum(0)]).to(torch.int32)
+    q = torch.randn(int(new.sum()), 4, 128, generator=g).bfloat16()
+    want = oracle.flash_attn_varlen_func(q, dec.k_cache, dec.v_cache, cu_q, cu_k, int(new.max()),
+                                         int(total.max()), softmax_scale=dec.softmax_scale,
+                                         causal=True, block_table=dec.block_table.clamp(min=0))
+    d = dec.to(DEV)
+    got = mops.flash_attn_varlen_func(q.to(DEV), d.k_cache, d.v_cache, max_seqlen_q=int(new.max()),
+                                      cu_seqlens_q=cu_q.to(DEV), max_seqlen_k=int(total.max()),
+                                      cu_seqlens_k=cu_k.to(DEV), softmax_scale=dec.softmax_scale,
+                                      causal=True, block_table=d.block_table)
+    close(got, want)
     assert mops.device_status() == 0
 
 
