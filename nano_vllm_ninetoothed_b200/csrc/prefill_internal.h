@@ -10,7 +10,7 @@ namespace b200mops {
 
 // Capacity of the tcgen05 kernel's in-kernel schedule tables.
 constexpr int kTc5MaxBatch = 1024;    // sequences per launch (longer batches are sliced)
-constexpr int kTc5MaxLevels = 256;    // 128-row query tiles per sequence (max_seqlen_q <= 32768)
+constexpr int kTc5MaxLevels = 512;    // 128-row query tiles per sequence (max_seqlen_q <= 65536)
 
 // Launches the tcgen05/TMEM kernel.  Requirements checked by the caller: head_dim 128,
 // batch <= kTc5MaxBatch, max_seqlen_q <= 128 * kTc5MaxLevels, and for paged K/V a page size

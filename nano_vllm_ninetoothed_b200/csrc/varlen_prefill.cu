@@ -315,7 +315,7 @@ extern "C" int b200mops_varlen_prefill(const b200mops_varlen_prefill_args* a, vo
         return B200MOPS_ERR_ALIGNMENT;
 
     // Kernel choice: the tcgen05 kernel takes everything except paged K/V whose page size is not
-    // a multiple of its 128-key tile and sequences of more than 32768 query rows; those stay on
+    // a multiple of its 128-key tile and sequences of more than 65536 query rows; those stay on
     // the mma.sync kernel.  B200MOPS_PREFILL_KERNEL=mma forces the latter (for A/B measurements).
     static const bool force_mma = [] {
         const char* e = getenv("B200MOPS_PREFILL_KERNEL");

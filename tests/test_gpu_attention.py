@@ -229,6 +229,28 @@ def test_prefill_many_short_sequences_paged(mops, oracle):
     assert mops.device_status() == 0
 
 
+def test_prefill_one_long_sequence_sample_rows(mops, oracle):
+    """One sequence of 40000 tokens (313 row tiles; longer than nano-vLLM's largest
+    max_model_len) plus a short one; sample rows are checked against the oracle as one-row
+    problems over their visible keys."""
+    n = 40000
+    p = W.make_prefill_case(seed=8, lens=[n, 300], hq=2, hkv=1, device=DEV)
+    out = mops.flash_attn_varlen_func(p.q, p.k, p.v, max_seqlen_q=p.max_seqlen,
+                                      cu_seqlens_q=p.cu_seqlens, max_seqlen_k=p.max_seqlen,
+                                      cu_seqlens_k=p.cu_seqlens, softmax_scale=p.softmax_scale,
+                                      causal=True)
+    assert mops.device_status() == 0
+    for r in (0, 1, 127, 128, 255, 256, 4095, 20000, 32767, 32768, n - 129, n - 1, n, n + 299):
+        begin = 0 if r < n else n
+        keys = slice(begin, r + 1)
+        cu_q = torch.tensor([0, 1], dtype=torch.int32)
+        cu_k = torch.tensor([0, r + 1 - begin], dtype=torch.int32)
+        want = oracle.flash_attn_varlen_func(p.q[r:r + 1].cpu(), p.k[keys].cpu(), p.v[keys].cpu(), cu_q,
+                                             cu_k, 1, r + 1 - begin, softmax_scale=p.softmax_scale,
+                                             causal=True)
+        close(out[r:r + 1], want)
+
+
 def test_prefill_non_causal_and_fp16(mops, oracle):
     run_prefill(mops, oracle, W.make_prefill_case(seed=3, lens=[50, 200, 129], hq=4, hkv=2), causal=False)
     run_prefill(mops, oracle, W.make_prefill_case(seed=3, lens=[50, 200, 129], hq=4, hkv=2,
