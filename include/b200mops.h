@@ -126,6 +126,22 @@ int b200mops_add_rmsnorm(const void* x, const void* residual, int64_t rows, int6
                          int dtype, void* stream);
 
 /* ------------------------------------------------------------------------
+ * linear: c[m, n] = a[m, k] . w[n, k]^T (+ bias[n]), fp32 accumulation, 16-bit
+ * in and out (the tcgen05 / TMEM GEMM of this library).  a, w and c are
+ * row-major with unit inner stride and row pitches lda, ldw, ldc (elements).
+ * a and w must be 16-byte aligned with pitches that are multiples of 8
+ * elements (B200MOPS_ERR_ALIGNMENT otherwise: the caller then keeps its
+ * library GEMM); c and bias have no alignment requirement.  status_word as
+ * in the attention calls (a wait that ran out sets B200MOPS_DEV_WAIT_TIMEOUT).
+ * Stands in for mops.linear: mops/torch/ops.py:5-7, called from
+ * nanovllm/layers/linear.py:53,75,152 and nanovllm/layers/embed_head.py:64.
+ * ---------------------------------------------------------------------- */
+int b200mops_linear(const void* a, int64_t lda, const void* w, int64_t ldw,
+                    const void* bias, void* c, int64_t ldc,
+                    int64_t m, int64_t n, int64_t k,
+                    int dtype, int32_t* status_word, void* stream);
+
+/* ------------------------------------------------------------------------
  * siluAndMul: out = cast(cast(silu(f32(x))) * y); x and y are [rows, n] views
  * with unit inner stride (the two halves of the gate_up activation).
  * Stands in for mops.siluAndMul: mops/torch/ops.py:32-34, called from

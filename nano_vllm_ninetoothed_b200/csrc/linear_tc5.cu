@@ -1,0 +1,286 @@
+// C = A W^T (+ bias) on the Blackwell tensor cores: a persistent, TMA-fed tcgen05 / TMEM GEMM for
+// the `linear` operator (activations [M, K] and weights [N, K], both K-contiguous, 16-bit;
+// fp32 accumulation; 16-bit output).
+//
+//   grid   one CTA per SM; each walks output tiles tile = blockIdx.x, + gridDim.x, ...  Tiles are
+//          128 x 256 and are numbered in groups of sixteen tile rows with the row index
+//          fastest, so the CTAs running at one time cover ~16 x 9 tiles and share their A and W
+//          tiles through L2 (a W tile is twice the size of an A tile, hence the oblong shape).
+//   warp 0 TMA producer: per 64-wide k-block one [128 x 64] box of A and one [256 x 64] box of W
+//          into a 4-stage ring of 128-byte-swizzled stages (48 KB each)
+//   warp 1 MMA issuer: four tcgen05.mma 128x256x16 per k-block, both operands K-major from shared
+//          memory, accumulator in tensor memory; tcgen05.commit releases the stage
+//   warps 2-5 epilogue: TMEM -> registers (one thread per output row), + bias, -> 16-bit -> global
+//   TMEM   two accumulators of 256 columns: the epilogue of tile i overlaps the k-loop of tile i+1
+//
+// Edges: TMA zero-fills boxes that reach past M, N or K (a zero k-tail adds nothing), the
+// epilogue guards rows and columns.  Every mbarrier wait is bounded; on a timeout the roles
+// fall through to the common exit, which frees the tensor memory.
+#include <type_traits>
+
+#include "attn_common.cuh"
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace b200mops {
+namespace {
+
+constexpr int kBM = 128, kBN = 256, kBK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = kBM * kBK * 2, kBBytes = kBN * kBK * 2, kStageBytes = kABytes + kBBytes;
+constexpr int kThreads = 192;
+constexpr int kGroupM = 16;
+constexpr int kOffBar = kStages * kStageBytes;
+constexpr int kNumBars = 2 * kStages + 4;     // full[4], empty[4], acc_full[2], acc_empty[2]
+constexpr int kSmemBytes = 1024 + kOffBar + kNumBars * 8 + 16;
+
+struct LinearParams {
+    void* c; int64_t ldc;
+    const void* bias;
+    int m, n, k;
+    int tiles_m, tiles_n;
+    int32_t* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                  const LinearParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~uintptr_t(1023));
+    const uint32_t sbase = smem_u32(smem);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * i; };
+    constexpr int FULL = 0, EMPTY = kStages, ACC_FULL = 2 * kStages, ACC_EMPTY = ACC_FULL + 2;
+
+    if (p.status && (*reinterpret_cast<volatile int32_t*>(p.status) & B200MOPS_DEV_WAIT_TIMEOUT)) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar(FULL + s), 1);
+            mbar_init(bar(EMPTY + s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(ACC_FULL + b), 1);
+            mbar_init(bar(ACC_EMPTY + b), 4);       // one arrival per epilogue warp
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tc5::tmem_alloc(smem_u32(tmem_slot), 512);
+        tc5::tmem_relinquish();
+    }
+    tc5::fence_before_sync();
+    __syncthreads();
+    tc5::fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int k_blocks = (p.k + kBK - 1) / kBK;
+    auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
+        const int per_group = kGroupM * p.tiles_n;
+        const int group = tile / per_group, in_group = tile - group * per_group;
+        const int first_m = group * kGroupM;
+        const int rows = min(kGroupM, p.tiles_m - first_m);
+        m_blk = first_m + in_group % rows;
+        n_blk = in_group / rows;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_a);
+            tma_prefetch_desc(&tm_w);
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                int m_blk, n_blk;
+                tile_coords(tile, m_blk, n_blk);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % kStages, round = it / kStages;
+                    if (round > 0 && !(ok = mbar_wait(bar(EMPTY + s), (uint32_t)(round - 1) & 1u, p.status))) break;
+                    const uint32_t dst = sbase + s * kStageBytes;
+                    mbar_arrive_expect_tx(bar(FULL + s), kStageBytes);
+                    tma_load_2d(dst, &tm_a, bar(FULL + s), kb * kBK, m_blk * kBM);
+                    tma_load_2d(dst + kABytes, &tm_w, bar(FULL + s), kb * kBK, n_blk * kBN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr int fmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+        constexpr uint32_t idesc = tc5::instr_desc_f16(fmt, kBM, kBN, 0, 0);
+        const bool leader = tc5::elect_one();
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem, 0);
+        const uint64_t da = tc5::smem_desc_sw128(sbase, 16, 1024);
+        const uint64_t db = tc5::smem_desc_sw128(sbase + kABytes, 16, 1024);
+        auto wait = [&](int b, uint32_t parity) {
+            const bool done = mbar_wait(bar(b), parity & 1u, p.status);
+            return __all_sync(0xffffffffu, done);
+        };
+        int it = 0, tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tcount) {
+            const int ab = tcount & 1, around = tcount >> 1;
+            // the epilogue must have drained this accumulator (two tiles ago)
+            if (around > 0 && !(ok = wait(ACC_EMPTY + ab, around - 1))) break;
+            tc5::fence_after_sync();
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % kStages;
+                if (!(ok = wait(FULL + s, it / kStages))) break;
+                tc5::fence_after_sync();
+                const uint32_t soff = (uint32_t)(s * kStageBytes) >> 4;
+                if (leader) {
+#pragma unroll
+                    for (int ks = 0; ks < kBK / 16; ++ks)
+                        tc5::mma_ss(tm + ab * kBN, da + soff + 2 * ks, db + soff + 2 * ks, idesc,
+                                    (kb | ks) != 0 ? 1u : 0u);
+                    tc5::commit(bar(EMPTY + s));        // the stage is free once these MMAs have read it
+                }
+            }
+            if (!ok) break;
+            if (leader) tc5::commit(bar(ACC_FULL + ab));
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue warps
+        const int q = warp & 3;                         // TMEM lane quarter this warp may touch
+        const uint32_t lane_base = (uint32_t)(32 * q) << 16;
+        const T* bias = reinterpret_cast<const T*>(p.bias);
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(p.c) & 15u) == 0 && (p.ldc % 8) == 0;
+        const bool vec32_ok = (reinterpret_cast<uintptr_t>(p.c) & 31u) == 0 && (p.ldc % 16) == 0;
+        int tcount = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tcount) {
+            int m_blk, n_blk;
+            tile_coords(tile, m_blk, n_blk);
+            const int ab = tcount & 1, around = tcount >> 1;
+            ok = mbar_wait(bar(ACC_FULL + ab), (uint32_t)around & 1u, p.status);
+            if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+            tc5::fence_after_sync();
+            const int64_t row = (int64_t)m_blk * kBM + q * 32 + lane;
+            T* crow = reinterpret_cast<T*>(p.c) + row * p.ldc;
+#pragma unroll 1
+            for (int cc = 0; cc < kBN / 32; ++cc) {
+                uint32_t v[32];
+                tc5::ld32(tmem + lane_base + ab * kBN + cc * 32, v);
+                tc5::wait_ld();
+                const int col0 = n_blk * kBN + cc * 32;
+                if (row < p.m && col0 < p.n) {
+                    if (bias) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < p.n)
+                                v[i] = __float_as_uint(__uint_as_float(v[i]) + DType<T>::to_f32(__ldg(bias + col0 + i)));
+                    }
+                    if (vec32_ok && col0 + 32 <= p.n) {
+                        // 32-byte stores: a thread owns 64 contiguous bytes of its row, i.e. two
+                        // whole 32-byte sectors
+#pragma unroll
+                        for (int i = 0; i < 32; i += 16) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                w[j] = pack2<T>(__uint_as_float(v[i + 2 * j]), __uint_as_float(v[i + 2 * j + 1]));
+                            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                         ::"l"(crow + col0 + i), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                                           "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                        }
+                    } else if (vec_ok && col0 + 32 <= p.n) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 w;
+                            w.x = pack2<T>(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                            w.y = pack2<T>(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                            w.z = pack2<T>(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                            w.w = pack2<T>(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                            *reinterpret_cast<uint4*>(crow + col0 + i) = w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < p.n) crow[col0 + i] = DType<T>::from_f32(__uint_as_float(v[i]));
+                    }
+                }
+            }
+            // the accumulator is in registers / memory: the MMA warp may reuse it
+            tc5::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(ACC_EMPTY + ab));
+        }
+    }
+
+    // ---------------------------------------------------------------- common exit
+    __syncwarp();
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc5::fence_after_sync();
+        tc5::tmem_dealloc(tmem, 512);
+    }
+}
+
+}  // namespace
+}  // namespace b200mops
+
+using namespace b200mops;
+
+extern "C" int b200mops_linear(const void* a, int64_t lda, const void* w, int64_t ldw,
+                               const void* bias, void* c, int64_t ldc, int64_t m, int64_t n,
+                               int64_t k, int dtype, int32_t* status_word, void* stream) {
+    if (dtype != B200MOPS_BF16 && dtype != B200MOPS_F16) return B200MOPS_ERR_DTYPE;
+    if (m < 0 || n <= 0 || k <= 0 || m > INT32_MAX - kBM || n > INT32_MAX - kBN || k > INT32_MAX - kBK)
+        return B200MOPS_ERR_SHAPE;
+    if (m == 0) return B200MOPS_OK;
+    if (!a || !w || !c) return B200MOPS_ERR_NULL_POINTER;
+    if (lda < k || ldw < k || ldc < n) return B200MOPS_ERR_STRIDE;
+    // TMA: 16-byte aligned bases and row pitches (checked again by the encoder)
+    if (lda % 8 != 0 || ldw % 8 != 0 || !aligned16(a) || !aligned16(w)) return B200MOPS_ERR_ALIGNMENT;
+
+    CUtensorMap tm_a, tm_w;
+    {
+        const uint64_t dims[2] = {(uint64_t)k, (uint64_t)m};
+        const uint64_t st[1] = {(uint64_t)lda * 2};
+        const uint32_t box[2] = {(uint32_t)kBK, (uint32_t)kBM};
+        const int rc = encode_map_16bit(&tm_a, dtype, a, 2, dims, st, box);
+        if (rc != B200MOPS_OK) return rc;
+    }
+    {
+        const uint64_t dims[2] = {(uint64_t)k, (uint64_t)n};
+        const uint64_t st[1] = {(uint64_t)ldw * 2};
+        const uint32_t box[2] = {(uint32_t)kBK, (uint32_t)kBN};
+        const int rc = encode_map_16bit(&tm_w, dtype, w, 2, dims, st, box);
+        if (rc != B200MOPS_OK) return rc;
+    }
+    LinearParams p;
+    p.c = c; p.ldc = ldc; p.bias = bias;
+    p.m = (int)m; p.n = (int)n; p.k = (int)k;
+    p.tiles_m = (int)((m + kBM - 1) / kBM);
+    p.tiles_n = (int)((n + kBN - 1) / kBN);
+    p.status = status_word;
+    if ((int64_t)p.tiles_m * p.tiles_n > INT32_MAX) return B200MOPS_ERR_SHAPE;
+
+    static int sm_count[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200MOPS_ERR_DEVICE;
+    if (sm_count[dev] == 0 &&
+        cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return B200MOPS_ERR_DEVICE;
+    const int tiles = p.tiles_m * p.tiles_n;
+    const dim3 grid((unsigned)(tiles < sm_count[dev] ? tiles : sm_count[dev]));
+    cudaStream_t st = as_stream(stream);
+    if (dtype == B200MOPS_BF16) {
+        if (cudaFuncSetAttribute(linear_tc5_kernel<__nv_bfloat16>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return B200MOPS_ERR_LAUNCH;
+        linear_tc5_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, st>>>(tm_a, tm_w, p);
+    } else {
+        if (cudaFuncSetAttribute(linear_tc5_kernel<__half>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+            return B200MOPS_ERR_LAUNCH;
+        linear_tc5_kernel<__half><<<grid, kThreads, kSmemBytes, st>>>(tm_a, tm_w, p);
+    }
+    return launch_status();
+}

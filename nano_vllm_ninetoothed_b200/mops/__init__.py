@@ -77,12 +77,38 @@ def reset_device_status(device=None) -> None:
         w.zero_()
 
 
-# --------------------------------------------------------------------------- library GEMM
+# --------------------------------------------------------------------------- GEMM
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
     """`x @ weight.T (+ bias)` through cuBLAS, exactly as the reference's torch backend does
     (mops/torch/ops.py:5-7); a plain library GEMM, not one of this package's kernels."""
     _need_cuda(x, weight)
     return torch.nn.functional.linear(x, weight, bias)
+
+
+def linear_tc5(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """`x @ weight.T (+ bias)` with this library's tcgen05 / TMEM GEMM (same contract as `linear`,
+    mops/torch/ops.py:5-7): x `[..., K]`, weight `[N, K]`, bias `[N]`, 16-bit, fp32 accumulation.
+    Raises for operands the kernel cannot take (unaligned base or pitch, other dtypes)."""
+    dev = _need_cuda(x, weight)
+    if x.dtype != weight.dtype or (bias is not None and bias.dtype != x.dtype):
+        raise RuntimeError("b200 mops: linear_tc5 needs x, weight and bias of one 16-bit dtype")
+    k = x.shape[-1]
+    if weight.dim() != 2 or weight.shape[1] != k:
+        raise RuntimeError(f"b200 mops: weight {tuple(weight.shape)} does not match x[..., {k}]")
+    x2 = x.reshape(-1, k)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    if weight.stride(-1) != 1:
+        weight = weight.contiguous()
+    if bias is not None:
+        bias = bias.contiguous()
+    n = weight.shape[0]
+    out = torch.empty((x2.shape[0], n), dtype=x.dtype, device=dev)
+    _cabi.check("b200mops_linear", _cabi.lib.b200mops_linear(
+        x2.data_ptr(), x2.stride(0) if x2.shape[0] > 1 else k, weight.data_ptr(), weight.stride(0),
+        bias.data_ptr() if bias is not None else None, out.data_ptr(), n, x2.shape[0], n, k,
+        _dtype(x), _status_word(dev), _stream(dev)))
+    return out.view(*x.shape[:-1], n)
 
 
 # The reference's torch backend has no `softmax` either (mops/registry.py:36-39 returns None),

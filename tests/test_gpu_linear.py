@@ -1,0 +1,89 @@
+"""`linear_tc5` (the tcgen05 / TMEM GEMM behind `b200mops_linear`) against a plain fp32 matmul of
+the same 16-bit operands, and against the CPU oracle's `linear` (mops/torch/ops.py:5-7).
+
+Tolerance: the kernel accumulates in fp32 and rounds once to the 16-bit output type, so it may
+differ from the fp32 product by one rounding of the output (relative 2^-8 for bf16, 2^-11 for
+fp16) plus accumulation-order noise; the oracle (a CPU bf16 GEMM) is itself only that close."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _case(m, n, k, dtype=torch.bfloat16, bias=False, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=g).to(dtype)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(dtype)
+    b = torch.randn(n, generator=g).to(dtype) if bias else None
+    return x, w, b
+
+
+def _check(got, x, w, b, dtype):
+    want = x.float() @ w.float().T
+    if b is not None:
+        want = want + b.float()
+    rel = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    torch.testing.assert_close(got.float().cpu(), want, rtol=rel, atol=rel * want.abs().max().item() * 0.25)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (1, 256, 64), (100, 200, 72), (257, 520, 136),
+                                   (300, 1000, 328), (640, 768, 1024), (129, 257, 8), (2048, 1024, 4096)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_shapes_and_edges(mops, m, n, k, bias):
+    """Tile-aligned and ragged M, N, K (tails in every dimension are zero-filled by TMA and
+    guarded in the epilogue), with and without bias."""
+    x, w, b = _case(m, n, k, bias=bias, seed=m + n + k)
+    got = mops.linear_tc5(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None)
+    assert got.shape == (m, n) and got.dtype == torch.bfloat16
+    _check(got, x, w, b, torch.bfloat16)
+    assert mops.device_status() == 0
+
+
+def test_linear_fp16_and_leading_dims(mops):
+    x, w, b = _case(6 * 50, 384, 256, dtype=torch.float16, bias=True, seed=3)
+    got = mops.linear_tc5(x.view(6, 50, 256).to(DEV), w.to(DEV), b.to(DEV))
+    assert got.shape == (6, 50, 384)
+    _check(got.view(-1, 384), x, w, b, torch.float16)
+
+
+def test_linear_strided_operands(mops):
+    """x is a column slice of a wider activation (row pitch > K) and the weight a row/column
+    slice of a fused matrix, as the qkv / gate_up layouts produce them."""
+    g = torch.Generator().manual_seed(5)
+    big_x = torch.randn(333, 1024, generator=g).bfloat16()
+    big_w = (torch.randn(700, 768, generator=g) * 0.05).bfloat16()
+    x, w = big_x[:, 256:768], big_w[100:612, 128:640]
+    got = mops.linear_tc5(big_x.to(DEV)[:, 256:768], big_w.to(DEV)[100:612, 128:640])
+    _check(got, x, w, None, torch.bfloat16)
+
+
+def test_linear_matches_oracle_and_library(mops, oracle):
+    x, w, b = _case(512, 1536, 1024, bias=True, seed=9)
+    got = mops.linear_tc5(x.to(DEV), w.to(DEV), b.to(DEV))
+    lib = mops.linear(x.to(DEV), w.to(DEV), b.to(DEV))
+    want = oracle.linear(x, w, b)
+    torch.testing.assert_close(got.float().cpu(), want.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got.float(), lib.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_linear_rejects_what_it_cannot_take(mops):
+    x = torch.randn(64, 100, device=DEV).bfloat16()          # row pitch 200 B: not a multiple of 16
+    w = torch.randn(32, 100, device=DEV).bfloat16()
+    with pytest.raises(Exception):
+        mops.linear_tc5(x, w)
+    with pytest.raises(Exception):
+        mops.linear_tc5(x.float(), w.float())
+    assert mops.linear_tc5(x[:0, :96].contiguous(), w[:, :96].contiguous()).shape == (0, 32)
+
+
+def test_linear_large_sample(mops):
+    """Prefill-sized problem (8192 x 6144 x 4096); a sample of rows is checked in fp32."""
+    g = torch.Generator(device=DEV).manual_seed(1)
+    x = torch.randn(8192, 4096, generator=g, device=DEV).bfloat16()
+    w = (torch.randn(6144, 4096, generator=g, device=DEV) * 0.02).bfloat16()
+    got = mops.linear_tc5(x, w)
+    rows = torch.tensor([0, 1, 127, 128, 4095, 4096, 8191], device=DEV)
+    want = x[rows].float() @ w.float().T
+    torch.testing.assert_close(got[rows].float(), want, rtol=2.0 ** -7, atol=2.0 ** -7 * want.abs().max().item() * 0.25)
+    assert mops.device_status() == 0
