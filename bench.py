@@ -328,6 +328,25 @@ def bench_side_ops(mops, dev, rank: int, world: int, steps: int, warmup: int, pk
     gbs = (256 * 151936 * 2) / (ms * 1e-3) / 1e9
     out["sampler_forward"] = {"rows": 256, "vocab": 151936, "gbs": gbs, "ms": ms,
                               "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
+    del logit_sets
+    # linear: this library's tcgen05 GEMM next to the library GEMM the `linear` name is bound to,
+    # at the Qwen3-8B qkv projection of the prefill workload (M = its 34.8 k tokens) and of a
+    # 256-sequence decode step (weights rotate over sets larger than L2)
+    gdev = torch.Generator(device=dev).manual_seed(11)
+    m_pre = sum(W.config_lens("prefill_8b"))
+    lin = {}
+    for name, m, n, k, copies in (("prefill_qkv", m_pre, 6144, 4096, 1), ("decode_qkv", 256, 6144, 4096, 4)):
+        xs = [torch.randn(m, k, generator=gdev, device=dev).bfloat16() for _ in range(copies)]
+        ws = [(torch.randn(n, k, generator=gdev, device=dev) * 0.02).bfloat16() for _ in range(copies)]
+        reps = 2 if m > 4096 else 8
+        own = per_call_ms([(lambda i=i: mops.linear_tc5(xs[i % copies], ws[i % copies])) for i in range(reps)])
+        lib = per_call_ms([(lambda i=i: mops.linear(xs[i % copies], ws[i % copies])) for i in range(reps)])
+        fl = 2.0 * m * n * k
+        lin[name] = {"m": m, "n": n, "k": k, "tflops": fl / (own * 1e-3) / 1e12, "ms": own,
+                     "frac_of_bf16_peak": fl / (own * 1e-3) / 1e12 / pk["bf16_tflops"],
+                     "cublas_tflops": fl / (lib * 1e-3) / 1e12, "cublas_ms": lib}
+        del xs, ws
+    out["linear_tc5"] = lin
     out["timing"] = "CUDA-graph replay of the calls over rotating input sets, events around the replays"
     return out
 

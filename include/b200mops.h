@@ -131,15 +131,21 @@ int b200mops_add_rmsnorm(const void* x, const void* residual, int64_t rows, int6
  * row-major with unit inner stride and row pitches lda, ldw, ldc (elements).
  * a and w must be 16-byte aligned with pitches that are multiples of 8
  * elements (B200MOPS_ERR_ALIGNMENT otherwise: the caller then keeps its
- * library GEMM); c and bias have no alignment requirement.  status_word as
+ * library GEMM); c and bias have no alignment requirement.  Problems with
+ * few output tiles (decode-time m) are split along k and need
+ * b200mops_linear_workspace_bytes(m, n, k) bytes of 16-byte aligned device
+ * scratch (0 for problems that are not split; without it the call still
+ * works, unsplit).  status_word as
  * in the attention calls (a wait that ran out sets B200MOPS_DEV_WAIT_TIMEOUT).
  * Stands in for mops.linear: mops/torch/ops.py:5-7, called from
  * nanovllm/layers/linear.py:53,75,152 and nanovllm/layers/embed_head.py:64.
  * ---------------------------------------------------------------------- */
+size_t b200mops_linear_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int b200mops_linear(const void* a, int64_t lda, const void* w, int64_t ldw,
                     const void* bias, void* c, int64_t ldc,
                     int64_t m, int64_t n, int64_t k,
-                    int dtype, int32_t* status_word, void* stream);
+                    int dtype, void* workspace, size_t workspace_bytes,
+                    int32_t* status_word, void* stream);
 
 /* ------------------------------------------------------------------------
  * siluAndMul: out = cast(cast(silu(f32(x))) * y); x and y are [rows, n] views

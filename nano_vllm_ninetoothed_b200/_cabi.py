@@ -28,6 +28,7 @@ EXPORTED_SYMBOLS = (
     "b200mops_embedding",
     "b200mops_rmsnorm",
     "b200mops_add_rmsnorm",
+    "b200mops_linear_workspace_bytes",
     "b200mops_linear",
     "b200mops_silu_mul",
     "b200mops_rope_neox",
@@ -86,7 +87,9 @@ _SIGNATURES = {
     "b200mops_rmsnorm": (C.c_int, [_vp, _i64, _i64, _i64, _i64, _vp, _f32, _vp, _i64, C.c_int, _vp]),
     "b200mops_add_rmsnorm": (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, _f32, _vp, _vp,
                                        C.c_int, _vp]),
-    "b200mops_linear": (C.c_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, C.c_int, _vp, _vp]),
+    "b200mops_linear_workspace_bytes": (_sz, [_i64, _i64, _i64]),
+    "b200mops_linear": (C.c_int, [_vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _i64, C.c_int, _vp, _sz,
+                                  _vp, _vp]),
     "b200mops_silu_mul": (C.c_int, [_vp, _vp, _i64, _i64, _i64, _i64, _vp, C.c_int, _vp]),
     "b200mops_rope_neox": (C.c_int, [_vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _i64, _vp,
                                      C.c_int, _vp]),

@@ -13,6 +13,10 @@
 //   warps 2-5 epilogue: TMEM -> registers (one thread per output row), + bias, -> 16-bit -> global
 //   TMEM   two accumulators of 256 columns: the epilogue of tile i overlaps the k-loop of tile i+1
 //
+// Skinny problems (fewer tiles than half the SMs: decode-time M) are split along K: work unit
+// (tile, split) computes a slice of the k-blocks, the epilogue writes fp32 partial tiles to the
+// caller's workspace and `linear_splitk_reduce_kernel` adds them up (+ bias) into the output.
+//
 // Edges: TMA zero-fills boxes that reach past M, N or K (a zero k-tail adds nothing), the
 // epilogue guards rows and columns.  Every mbarrier wait is bounded; on a timeout the roles
 // fall through to the common exit, which frees the tensor memory.
@@ -39,6 +43,8 @@ struct LinearParams {
     const void* bias;
     int m, n, k;
     int tiles_m, tiles_n;
+    int splits, kb_per_split;       // K split: work units = tiles * splits
+    float* partial;                 // [splits][m][n] fp32 when splits > 1
     int32_t* status;
 };
 
@@ -78,8 +84,16 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     tc5::fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_units = p.tiles_m * p.tiles_n * p.splits;
     const int k_blocks = (p.k + kBK - 1) / kBK;
+    // k-blocks [kb0, kb1) of work unit `unit`; the splits of one tile are neighbouring units, so
+    // they run at the same time on different SMs
+    auto unit_range = [&](int unit, int& tile, int& split, int& kb0, int& kb1) {
+        tile = unit / p.splits;
+        split = unit - tile * p.splits;
+        kb0 = split * p.kb_per_split;
+        kb1 = min(k_blocks, kb0 + p.kb_per_split);
+    };
     auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
         const int per_group = kGroupM * p.tiles_n;
         const int group = tile / per_group, in_group = tile - group * per_group;
@@ -96,10 +110,11 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             tma_prefetch_desc(&tm_w);
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                int m_blk, n_blk;
+            for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x) {
+                int tile, split, kb0, kb1, m_blk, n_blk;
+                unit_range(unit, tile, split, kb0, kb1);
                 tile_coords(tile, m_blk, n_blk);
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % kStages, round = it / kStages;
                     if (round > 0 && !(ok = mbar_wait(bar(EMPTY + s), (uint32_t)(round - 1) & 1u, p.status))) break;
                     const uint32_t dst = sbase + s * kStageBytes;
@@ -123,12 +138,14 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         };
         int it = 0, tcount = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tcount) {
+        for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x, ++tcount) {
+            int tile, split, kb0, kb1;
+            unit_range(unit, tile, split, kb0, kb1);
             const int ab = tcount & 1, around = tcount >> 1;
             // the epilogue must have drained this accumulator (two tiles ago)
             if (around > 0 && !(ok = wait(ACC_EMPTY + ab, around - 1))) break;
             tc5::fence_after_sync();
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int s = it % kStages;
                 if (!(ok = wait(FULL + s, it / kStages))) break;
                 tc5::fence_after_sync();
@@ -137,7 +154,7 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
 #pragma unroll
                     for (int ks = 0; ks < kBK / 16; ++ks)
                         tc5::mma_ss(tm + ab * kBN, da + soff + 2 * ks, db + soff + 2 * ks, idesc,
-                                    (kb | ks) != 0 ? 1u : 0u);
+                                    (kb > kb0 || ks > 0) ? 1u : 0u);
                     tc5::commit(bar(EMPTY + s));        // the stage is free once these MMAs have read it
                 }
             }
@@ -153,8 +170,9 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         const bool vec32_ok = (reinterpret_cast<uintptr_t>(p.c) & 31u) == 0 && (p.ldc % 16) == 0;
         int tcount = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++tcount) {
-            int m_blk, n_blk;
+        for (int unit = blockIdx.x; ok && unit < num_units; unit += gridDim.x, ++tcount) {
+            int tile, split, kb0, kb1, m_blk, n_blk;
+            unit_range(unit, tile, split, kb0, kb1);
             tile_coords(tile, m_blk, n_blk);
             const int ab = tcount & 1, around = tcount >> 1;
             ok = mbar_wait(bar(ACC_FULL + ab), (uint32_t)around & 1u, p.status);
@@ -168,7 +186,21 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                 tc5::ld32(tmem + lane_base + ab * kBN + cc * 32, v);
                 tc5::wait_ld();
                 const int col0 = n_blk * kBN + cc * 32;
-                if (row < p.m && col0 < p.n) {
+                if (p.splits > 1) {
+                    // fp32 partial tile; the reduce kernel adds the bias
+                    if (row < p.m && col0 < p.n) {
+                        float* prow = p.partial + ((int64_t)split * p.m + row) * p.n + col0;
+                        if ((p.n & 3) == 0 && col0 + 32 <= p.n) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4)
+                                *reinterpret_cast<uint4*>(prow + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (col0 + i < p.n) prow[i] = __uint_as_float(v[i]);
+                        }
+                    }
+                } else if (row < p.m && col0 < p.n) {
                     if (bias) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
@@ -222,14 +254,67 @@ linear_tc5_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     }
 }
 
+// out[r, c] = cast(sum over splits of partial[s][r][c] + bias[c]); one thread per four columns.
+template <typename T>
+__global__ void __launch_bounds__(256)
+linear_splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t m, int n,
+                            const T* __restrict__ bias, T* __restrict__ c, int64_t ldc) {
+    const int n4 = (n + 3) / 4;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= m * n4) return;
+    const int64_t r = idx / n4;
+    const int c0 = (int)(idx - r * n4) * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool full = (n & 3) == 0;
+    for (int s = 0; s < splits; ++s) {
+        const float* src = partial + ((int64_t)s * m + r) * n + c0;
+        if (full) {
+            const float4 v = *reinterpret_cast<const float4*>(src);
+            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        } else {
+            for (int i = 0; i < 4; ++i)
+                if (c0 + i < n) acc[i] += src[i];
+        }
+    }
+    for (int i = 0; i < 4; ++i)
+        if (c0 + i < n) {
+            const float b = bias ? DType<T>::to_f32(bias[c0 + i]) : 0.f;
+            c[r * ldc + c0 + i] = DType<T>::from_f32(acc[i] + b);
+        }
+}
+
+// K split of a skinny problem: as many splits as fill the machine once, at least four k-blocks
+// each; 1 = no split.
+void linear_split(int64_t m, int64_t n, int64_t k, int* splits, int* kb_per_split) {
+    const int64_t tiles = ((m + kBM - 1) / kBM) * ((n + kBN - 1) / kBN);
+    const int k_blocks = (int)((k + kBK - 1) / kBK);
+    int s = 1;
+    if (tiles * 2 <= kNumSMs) {
+        s = (int)(kNumSMs / tiles);
+        if (s > k_blocks / 4) s = k_blocks / 4;
+        if (s < 1) s = 1;
+    }
+    const int per = (k_blocks + s - 1) / s;
+    *kb_per_split = per;
+    *splits = (k_blocks + per - 1) / per;      // no empty split
+}
+
 }  // namespace
 }  // namespace b200mops
 
 using namespace b200mops;
 
+extern "C" size_t b200mops_linear_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || n <= 0 || k <= 0) return 0;
+    int splits, per;
+    linear_split(m, n, k, &splits, &per);
+    return splits > 1 ? (size_t)splits * (size_t)m * (size_t)n * sizeof(float) : 0;
+}
+
 extern "C" int b200mops_linear(const void* a, int64_t lda, const void* w, int64_t ldw,
                                const void* bias, void* c, int64_t ldc, int64_t m, int64_t n,
-                               int64_t k, int dtype, int32_t* status_word, void* stream) {
+                               int64_t k, int dtype, void* workspace, size_t workspace_bytes,
+                               int32_t* status_word, void* stream) {
     if (dtype != B200MOPS_BF16 && dtype != B200MOPS_F16) return B200MOPS_ERR_DTYPE;
     if (m < 0 || n <= 0 || k <= 0 || m > INT32_MAX - kBM || n > INT32_MAX - kBN || k > INT32_MAX - kBK)
         return B200MOPS_ERR_SHAPE;
@@ -260,7 +345,14 @@ extern "C" int b200mops_linear(const void* a, int64_t lda, const void* w, int64_
     p.tiles_m = (int)((m + kBM - 1) / kBM);
     p.tiles_n = (int)((n + kBN - 1) / kBN);
     p.status = status_word;
-    if ((int64_t)p.tiles_m * p.tiles_n > INT32_MAX) return B200MOPS_ERR_SHAPE;
+    if ((int64_t)p.tiles_m * p.tiles_n > INT32_MAX / 64) return B200MOPS_ERR_SHAPE;
+    linear_split(m, n, k, &p.splits, &p.kb_per_split);
+    if (p.splits > 1 && (!workspace || workspace_bytes < (size_t)p.splits * (size_t)m * (size_t)n * sizeof(float) ||
+                         (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0)) {
+        p.splits = 1;                              // no usable workspace: one unit per tile
+        p.kb_per_split = (int)((k + kBK - 1) / kBK);
+    }
+    p.partial = reinterpret_cast<float*>(workspace);
 
     static int sm_count[64] = {};
     int dev = 0;
@@ -268,8 +360,8 @@ extern "C" int b200mops_linear(const void* a, int64_t lda, const void* w, int64_
     if (sm_count[dev] == 0 &&
         cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         return B200MOPS_ERR_DEVICE;
-    const int tiles = p.tiles_m * p.tiles_n;
-    const dim3 grid((unsigned)(tiles < sm_count[dev] ? tiles : sm_count[dev]));
+    const int units = p.tiles_m * p.tiles_n * p.splits;
+    const dim3 grid((unsigned)(units < sm_count[dev] ? units : sm_count[dev]));
     cudaStream_t st = as_stream(stream);
     if (dtype == B200MOPS_BF16) {
         if (cudaFuncSetAttribute(linear_tc5_kernel<__nv_bfloat16>,
@@ -281,6 +373,17 @@ extern "C" int b200mops_linear(const void* a, int64_t lda, const void* w, int64_
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
             return B200MOPS_ERR_LAUNCH;
         linear_tc5_kernel<__half><<<grid, kThreads, kSmemBytes, st>>>(tm_a, tm_w, p);
+    }
+    if (p.splits > 1) {
+        if (cudaGetLastError() != cudaSuccess) return B200MOPS_ERR_LAUNCH;
+        const int64_t work = m * ((n + 3) / 4);
+        const unsigned blocks = (unsigned)((work + 255) / 256);
+        if (dtype == B200MOPS_BF16)
+            linear_splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+                p.partial, p.splits, m, (int)n, (const __nv_bfloat16*)bias, (__nv_bfloat16*)c, ldc);
+        else
+            linear_splitk_reduce_kernel<__half><<<blocks, 256, 0, st>>>(
+                p.partial, p.splits, m, (int)n, (const __half*)bias, (__half*)c, ldc);
     }
     return launch_status();
 }

@@ -104,10 +104,12 @@ def linear_tc5(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None 
         bias = bias.contiguous()
     n = weight.shape[0]
     out = torch.empty((x2.shape[0], n), dtype=x.dtype, device=dev)
+    ws_bytes = _cabi.lib.b200mops_linear_workspace_bytes(x2.shape[0], n, k)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
     _cabi.check("b200mops_linear", _cabi.lib.b200mops_linear(
         x2.data_ptr(), x2.stride(0) if x2.shape[0] > 1 else k, weight.data_ptr(), weight.stride(0),
         bias.data_ptr() if bias is not None else None, out.data_ptr(), n, x2.shape[0], n, k,
-        _dtype(x), _status_word(dev), _stream(dev)))
+        _dtype(x), ws.data_ptr() if ws is not None else None, ws_bytes, _status_word(dev), _stream(dev)))
     return out.view(*x.shape[:-1], n)
 
 

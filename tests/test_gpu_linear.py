@@ -40,6 +40,20 @@ def test_linear_shapes_and_edges(mops, m, n, k, bias):
     assert mops.device_status() == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 1024, 4096), (1, 512, 2048), (37, 1000, 1032), (256, 513, 1024),
+                                   (200, 2050, 12288)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_linear_skinny_problems_split_along_k(mops, m, n, k, bias):
+    """Decode-time shapes: few output tiles, so the kernel splits K over the SMs and a second
+    kernel adds the fp32 partial tiles (N not a multiple of 4 takes its scalar path)."""
+    from nano_vllm_ninetoothed_b200 import _cabi
+    assert _cabi.lib.b200mops_linear_workspace_bytes(m, n, k) > 0
+    x, w, b = _case(m, n, k, bias=bias, seed=m * 7 + n)
+    got = mops.linear_tc5(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None)
+    _check(got, x, w, b, torch.bfloat16)
+    assert mops.device_status() == 0
+
+
 def test_linear_fp16_and_leading_dims(mops):
     x, w, b = _case(6 * 50, 384, 256, dtype=torch.float16, bias=True, seed=3)
     got = mops.linear_tc5(x.view(6, 50, 256).to(DEV), w.to(DEV), b.to(DEV))
