@@ -25,6 +25,8 @@
 //   per KV tile j:   S_t = Q_t K_j^T  ->  softmax group t: row max, lazy rescale of O_t,
 //                    P_t = exp2(S_t*c - m)  ->  O_t += P_t V_j
 //   issue order:     S0(0) S1(0) | PV0(j) S0(j+1) PV1(j) S1(j+1) | ...
+//   P_t reaches the MMA warp in two instalments (keys 0-95, then 96-127), each with its own
+//   mbarrier, so most of PV_t is under way while the last exponentials are computed.
 //
 // Schedule: items are ordered by row-tile index descending (a later row tile has more KV tiles
 // under the causal mask), sequences sorted by length inside a level, head pairs innermost, and
