@@ -23,7 +23,7 @@ from .._cabi import PagedDecodeArgs, VarlenPrefillArgs, check, lib
 __all__ = [
     "linear", "rms_forward", "add_rms_forward", "softmax", "siluAndMul", "sampler_forward",
     "apply_rotary_emb", "embedding", "store_kvcache", "flash_attn_varlen_func",
-    "flash_attn_with_kvcache", "device_status", "reset_device_status",
+    "flash_attn_with_kvcache", "linear_tc5", "device_status", "reset_device_status",
 ]
 
 _DTYPES = {torch.bfloat16: _cabi.BF16, torch.float16: _cabi.F16, torch.float32: _cabi.F32}
