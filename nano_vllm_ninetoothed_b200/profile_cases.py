@@ -20,7 +20,8 @@ from . import workloads as W
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["decode", "prefill", "store", "add_rms", "embedding"])
+    ap.add_argument("op", choices=["decode", "prefill", "store", "add_rms", "embedding", "linear"])
+    ap.add_argument("--mnk", type=int, nargs=3, default=[8192, 6144, 4096], help="linear: M N K")
     ap.add_argument("--seqs", type=int, default=0)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--hkv", type=int, default=8)
@@ -45,6 +46,13 @@ def main() -> None:
                                                  cu_seqlens_q=p.cu_seqlens, max_seqlen_k=p.max_seqlen,
                                                  cu_seqlens_k=p.cu_seqlens, softmax_scale=p.softmax_scale,
                                                  causal=True)
+    elif a.op == "linear":
+        m, n, k = a.mnk
+        gen = torch.Generator(device=dev).manual_seed(0)
+        x = torch.randn(m, k, generator=gen, device=dev).bfloat16()
+        w = (torch.randn(n, k, generator=gen, device=dev) * 0.02).bfloat16()
+        units, unit = 2.0 * m * n * k / 1e12, "TFLOP"
+        fn = lambda: mops.linear_tc5(x, w)
     else:
         t = 8 * sum(W.config_lens("prefill_small"))     # ~65k tokens: footprint well above L2
         if a.op == "store":
