@@ -3,6 +3,7 @@
     python -m nano_vllm_ninetoothed_b200.profile_cases decode  [--seqs 64] [--iters 3]
     python -m nano_vllm_ninetoothed_b200.profile_cases prefill [--seqs 4]
     python -m nano_vllm_ninetoothed_b200.profile_cases store | add_rms | embedding
+    python -m nano_vllm_ninetoothed_b200.profile_cases linear  [--mnk 8192 6144 4096]
 
 The decode and prefill cases use the head shapes and length distributions of the large
 benchmark configurations with fewer sequences, so that the K/V footprint stays far above L2
