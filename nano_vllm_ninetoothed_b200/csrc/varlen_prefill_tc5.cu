@@ -81,20 +81,6 @@ constexpr int kOffSched = kOffBar + kNumBars * 8 + 16;     // schedule tables (u
 constexpr int kSchedBytes = (2 * kTc5MaxBatch + kTc5MaxLevels) * 2;
 constexpr int kSmemBytes = 1024 + kOffSched + kSchedBytes;
 
-#ifdef B200MOPS_TC5_TRACE
-// Development aid (not compiled by default): per-CTA cycle accounting of the MMA warp.
-// [cta][0] total cycles, [1] tiles, [2..7] cycles waiting on V, O_FREE, P0, Q+K, P1, items.
-__device__ long long g_tc5_acct[256][8];
-#define TC5_ACCT(slot, expr)                                             \
-    do {                                                                 \
-        const long long t_ = clock64();                                  \
-        expr;                                                            \
-        if (blockIdx.x < 256) acct[slot] += clock64() - t_;              \
-    } while (0)
-#else
-#define TC5_ACCT(slot, expr) do { expr; } while (0)
-#endif
-
 struct Tc5Params {
     void* out; int64_t out_stride_t, out_stride_h;
     const int32_t* cu_q; const int32_t* cu_k;
@@ -375,10 +361,6 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
             return false;
         };
-#ifdef B200MOPS_TC5_TRACE
-        long long acct[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        const long long t_begin = clock64();
-#endif
         Cursor cur = first_item();
         Item it{};
         bool have = false;
@@ -413,25 +395,25 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
             }
             const int nj = last ? 0 : j + 1;
             const bool next_is_last = more && (nj + 1 == nit.ntiles);
-            TC5_ACCT(2, ok = wait(V_FULL + s, g / kKVStages));
+            ok = wait(V_FULL + s, g / kKVStages);
             if (!ok) break;
             // the previous item's epilogue must have lifted O out of TMEM before PV(0) lands
-            if (j == 0 && n_act > 0) TC5_ACCT(3, ok = wait(O_FREE + 0, n_act - 1));
+            if (j == 0 && n_act > 0) ok = wait(O_FREE + 0, n_act - 1);
             if (!ok) break;
-            TC5_ACCT(4, ok = issue_pv(0, g, acc0));
+            ok = issue_pv(0, g, acc0);
             if (!ok) break;
             if (last && leader) tc5::commit(bar(O_DONE + 0));
             if (more) {
-                if (new_item) TC5_ACCT(5, ok = wait(Q_FULL, n_act + 1));
+                if (new_item) ok = wait(Q_FULL, n_act + 1);
                 if (!ok) break;
-                TC5_ACCT(5, ok = wait(K_FULL + sn, (g + 1) / kKVStages));
+                ok = wait(K_FULL + sn, (g + 1) / kKVStages);
                 if (!ok) break;
                 tc5::fence_after_sync();
                 issue_s(0, g + 1);
             }
-            if (j == 0 && n_act > 0) TC5_ACCT(3, ok = wait(O_FREE + 1, n_act - 1));
+            if (j == 0 && n_act > 0) ok = wait(O_FREE + 1, n_act - 1);
             if (!ok) break;
-            TC5_ACCT(6, ok = issue_pv(1, g, acc0));
+            ok = issue_pv(1, g, acc0);
             if (!ok) break;
             if (leader) {
                 tc5::commit(bar(V_EMPTY + s));
@@ -451,14 +433,6 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
                 it = nit;
             }
         }
-#ifdef B200MOPS_TC5_TRACE
-        if (lane == 0 && blockIdx.x < 256) {
-            acct[0] = clock64() - t_begin;
-            acct[1] = g + 1;
-            acct[7] = n_act + 1;
-            for (int i = 0; i < 8; ++i) g_tc5_acct[blockIdx.x][i] = acct[i];
-        }
-#endif
     } else {
         // ------------------------------------------------------------ softmax groups
         const int t = warp >> 2;                        // tile within the pair
@@ -638,11 +612,6 @@ varlen_prefill_tc5_kernel(const __grid_constant__ CUtensorMap tm_q,
 
 }  // namespace
 
-#ifdef B200MOPS_TC5_TRACE
-extern "C" int b200mops_debug_tc5_acct(long long* host_out) {
-    return cudaMemcpyFromSymbol(host_out, g_tc5_acct, sizeof(g_tc5_acct)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 int launch_varlen_prefill_tc5(const b200mops_varlen_prefill_args* a, const CUtensorMap& tm_q,
                               const CUtensorMap& tm_k, const CUtensorMap& tm_v, cudaStream_t st) {
