@@ -110,3 +110,27 @@ def test_decode_chunking_helpers(built_library):
     # argmax scratch: 8 bytes per (row, split)
     assert lib.b200mops_sample_argmax_workspace_bytes(8, 151936) % 8 == 0
     assert lib.b200mops_sample_argmax_workspace_bytes(0, 151936) == 0
+
+
+def test_linear_argument_checks_and_split_heuristic(built_library):
+    """`b200mops_linear` argument validation and the K-split workspace rule, neither of which
+    reaches a CUDA call."""
+    from nano_vllm_ninetoothed_b200 import _cabi
+    lib = _cabi.lib
+    ok = (16, 4096, 32, 4096, None, 48, 6144)        # a, lda, w, ldw, bias, c, ldc (fake aligned addresses)
+    assert lib.b200mops_linear(*ok, 128, 6144, 4096, 2, None, 0, None, None) == 2      # fp32: wrong dtype
+    assert lib.b200mops_linear(*ok, -1, 6144, 4096, 0, None, 0, None, None) == 3       # negative m
+    assert lib.b200mops_linear(*ok, 0, 6144, 4096, 0, None, 0, None, None) == 0        # empty problem
+    assert lib.b200mops_linear(None, 4096, 32, 4096, None, 48, 6144, 8, 6144, 4096, 0, None, 0, None, None) == 1
+    assert lib.b200mops_linear(16, 100, 32, 4096, None, 48, 6144, 8, 6144, 4096, 0, None, 0, None, None) == 4   # lda < k
+    # row pitch of 4100 elements is not a multiple of 16 bytes; base 18 is not 16-byte aligned
+    assert lib.b200mops_linear(16, 4100, 32, 4096, None, 48, 6144, 8, 6144, 4096, 0, None, 0, None, None) == 5
+    assert lib.b200mops_linear(18, 4096, 32, 4096, None, 48, 6144, 8, 6144, 4096, 0, None, 0, None, None) == 5
+    ws = lib.b200mops_linear_workspace_bytes
+    # prefill-sized problems fill the machine with whole tiles: no split, no workspace
+    assert ws(34816, 6144, 4096) == 0 and ws(8192, 8192, 8192) == 0
+    # 256 x 4096 x 12288: 2 x 16 tiles -> 4 splits of the 192 k-blocks, fp32 partial tiles
+    assert ws(256, 4096, 12288) == 4 * 256 * 4096 * 4
+    # a split holds at least four k-blocks, and degenerate sizes need nothing
+    assert ws(128, 256, 256) == 0 and ws(128, 256, 512) == 2 * 128 * 256 * 4
+    assert ws(0, 256, 512) == 0 and ws(128, 0, 512) == 0
