@@ -5,7 +5,9 @@ reference binds in mops/__init__.py:15-26 and that nanovllm/layers/* import at m
 There is no backend registry and no switch: every name is bound directly to a function that
 validates its tensors, allocates the outputs through torch (so calls stay CUDA-graph
 capturable) and launches one hand-written kernel on torch's current stream.  CPU tensors are
-rejected -- this backend has no CPU path.
+rejected -- this backend has no CPU path.  One name goes beyond the reference's list:
+`linear_tc5`, the library's own tcgen05 GEMM with the call signature of `linear` (which itself
+stays the cuBLAS call the reference's torch backend makes).
 
 Use it either as `nano_vllm_ninetoothed_b200.mops` or, for unmodified callers that say
 `from mops import ...`, after `nano_vllm_ninetoothed_b200.install_as_mops()`.
