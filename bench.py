@@ -244,17 +244,6 @@ def bench_side_ops(mops, dev, rank: int, world: int, steps: int, warmup: int, pk
     rotating over copies that together exceed L2 where one copy would fit in it)."""
     out = {}
 
-    def rotate(make, n_copies):
-        sets = [make(i) for i in range(n_copies)]
-        state = {"i": 0}
-
-        def step(fn):
-            def run():
-                fn(*sets[state["i"] % n_copies])
-                state["i"] += 1
-            return run
-        return step
-
     # varlen causal prefill, Qwen3-8B heads, 16 sequences in [256, 4096], KV-head sharded
     lens = W.config_lens("prefill_8b")
     full = W.make_prefill_case(seed=0, lens=lens, hq=HQ, hkv=HKV, device=dev)
